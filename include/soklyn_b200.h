@@ -1,0 +1,154 @@
+/*
+ * soklyn_b200 — C ABI of the B200 (sm_100a) DenseBlock / FeedForwardNetwork hot path.
+ *
+ * This is the boundary a host binding (Rust `extern "C"`, ctypes, ...) calls in place of
+ * the reference's PTX-module launches: every entry point below replaces one
+ * `GpuContext::gpu_*` method of Felix1G/soklyn and cites it. All pointers in `sk_dense`
+ * are DEVICE pointers borrowed for the duration of the call; the library never frees or
+ * keeps them. Calls are ordered on the context's stream and return without waiting for
+ * the GPU; `sk_sync` waits. No entry point allocates device memory after `sk_ctx_create`
+ * / `sk_ctx_reserve`.
+ *
+ * Matrices are row-major. Ordinals are the reference's kernel ABI
+ * (src/util/function.rs:33-39,65-72,104-116,153-164; LossFunc `as u32`).
+ */
+#ifndef SOKLYN_B200_H
+#define SOKLYN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes; the non-zero ones map onto the variants of src/util/log.rs:15-99. */
+enum {
+    SK_OK = 0,
+    SK_ERR_DRIVER = 1,                 /* Error::DriverError */
+    SK_ERR_MISMATCHED_DIMENSIONS = 2,  /* Error::MismatchedDimensions */
+    SK_ERR_ALLOCATION_LIMIT = 3,       /* Error::AllocationLimitExceeded */
+    SK_ERR_INVALID_CONFIGURATION = 4,  /* Error::InvalidConfiguration */
+    SK_ERR_INVALID_BATCH_SIZE = 5,     /* Error::InvalidBatchSize */
+    SK_ERR_TRAINING_MODE_REQUIRED = 6, /* Error::TrainingModeRequired */
+    SK_ERR_HARDWARE_CONSTRAINT = 7,    /* Error::HardwareConstraintViolation */
+    SK_ERR_UNSUPPORTED_CAST = 8,       /* Error::UnsupportedTypeCast */
+    SK_ERR_NULL_POINTER = 9,           /* no counterpart: a required pointer is NULL */
+    SK_ERR_WORKSPACE = 10,             /* no counterpart: scratch workspace too small */
+    SK_ERR_DEVICE_TIMEOUT = 11         /* no counterpart: a bounded device-side wait gave up */
+};
+
+enum { SK_F32 = 0, SK_F16 = 1, SK_BF16 = 2 };
+enum { SK_ACT_IDENTITY = 0, SK_ACT_SIGMOID = 1, SK_ACT_RELU = 2, SK_ACT_LEAKY_RELU = 3,
+       SK_ACT_TANH = 4, SK_ACT_SOFTMAX = 5, SK_ACT_SILU = 6, SK_ACT_MISH = 7 };
+enum { SK_NORM_DISABLED = 0, SK_NORM_RMS = 1, SK_NORM_LAYER = 2, SK_NORM_BATCH = 3 };
+enum { SK_OPT_SGD = 0, SK_OPT_ADAM = 1 };
+enum { SK_REGU_NONE = 0, SK_REGU_L1 = 1, SK_REGU_L2 = 2 };
+enum { SK_LOSS_MSE = 0, SK_LOSS_CROSS_ENTROPY = 1, SK_LOSS_BINARY_CROSS_ENTROPY = 2 };
+
+typedef struct sk_ctx sk_ctx;
+
+/* Optimiser hyper-parameters as src/io/device/ffn_device.rs:254-269 unpacks them:
+ * SGD{v_coeff, nesterov} -> (beta1, 0, 0, nesterov); Adam{m_coeff, v_coeff, epsilon}
+ * -> (beta1, beta2, epsilon, 0). */
+typedef struct {
+    uint32_t kind;
+    float beta1, beta2, epsilon;
+    uint32_t nesterov;
+} sk_optim;
+
+/* One DenseBlock's device state (src/mlp.rs:14-24, :232-241, :268-288). `T` below is
+ * the storage type named by `dtype`. In f32 mode the master_* pointers may be NULL or
+ * alias the parameter itself, as src/io/device.rs:262-272 does. Gradient-side pointers
+ * may be NULL for an inference-only block (is_training == 0). */
+typedef struct {
+    uint32_t dtype;                 /* SK_F32 / SK_F16 / SK_BF16 */
+    uint32_t K, N, max_batch;       /* inputs, outputs, rows of every cache tensor */
+    uint32_t is_training;
+    void *w, *b;                    /* T [K x N], T [N] */
+    float *master_w, *master_b;     /* f32 copies (16-bit modes) */
+    float *dv_w, *dv_b, *dm_w, *dm_b;
+    void *norm_w, *norm_b;          /* T [N] */
+    float *master_norm_w, *master_norm_b;
+    float *dv_norm_w, *dv_norm_b, *dm_norm_w, *dm_norm_b;
+    void *out, *predrop, *preact, *centered, *prenorm; /* T [max_batch x N] */
+    void *norm_rstd;                /* T [max(max_batch, N)] */
+    void *mask;                     /* T [max_batch x N] */
+    float *grad, *d_prenorm, *d_norm_w, *d_norm_b;     /* f32 [max_batch x N] */
+    void *d_prenorm_lp;             /* T [max_batch x N]: 16-bit copy of d_prenorm feeding the
+                                       tensor-core GEMMs; required in 16-bit modes, unused in f32 */
+    uint32_t norm, act;
+    float leaky_coeff;
+    uint32_t regu;
+    float regu_coeff, mask_coeff;
+    uint32_t tensor_id;             /* id of `w` (src/util/core.rs:84-88); seeds the dropout hash */
+} sk_dense;
+
+/* GpuContext::with_device_index (src/io/device.rs:164-183). tile_dim is kept for API
+ * compatibility: 16-bit modes still require 16 (src/io/device.rs:248-258), the kernels
+ * ignore it. `stream` is a cudaStream_t to run on, or NULL for a stream the context
+ * creates. workspace_bytes of scratch are allocated here (0 = default 64 MiB). */
+int sk_ctx_create(int device, uint32_t tile_dim, void *stream, size_t workspace_bytes, sk_ctx **out);
+void sk_ctx_destroy(sk_ctx *ctx);
+/* Replace the stream later calls are ordered on (no counterpart; the reference owns one stream). */
+int sk_ctx_set_stream(sk_ctx *ctx, void *stream);
+/* Grow the scratch workspace; never called implicitly. */
+int sk_ctx_reserve(sk_ctx *ctx, size_t workspace_bytes);
+/* CudaStream::synchronize as called after every launch in src/io/device/ffn_device.rs:75,110,136. */
+int sk_sync(sk_ctx *ctx);
+/* Text for a status code, and the detail of the last failure on this context. */
+const char *sk_status_string(int status);
+const char *sk_last_error(const sk_ctx *ctx);
+/* Number of kernels this context has launched since creation (for launch accounting). */
+uint64_t sk_launch_count(const sk_ctx *ctx);
+
+/* scramble_seed (src/util/core.rs:90-94). */
+uint32_t sk_scramble_seed(uint32_t step, uint32_t tensor_id);
+
+/* GpuContext::gpu_forward_pass (src/io/device/ffn_device.rs:12-139), with the checks of
+ * DenseBlock::forward (src/mlp.rs:492-580). x is T [x_rows x K]; the first `batch` rows are
+ * used. row_offset is added to the row index hashed by dropout (0 on one device; the first
+ * global row of this shard under data parallelism). */
+int sk_dense_forward(sk_ctx *ctx, const sk_dense *layer, const void *x, uint32_t x_rows,
+                     uint32_t batch, uint32_t use_dropout, uint32_t step, uint32_t row_offset);
+
+/* GpuContext::gpu_compute_output_layer_error (src/io/device/ffn_device.rs:141-231) with the
+ * checks of DenseBlock::compute_loss (src/mlp.rs:756-821). Works on `rows` rows of the block's
+ * `out` (the reference always passes out.rows() == max_batch); target is T [>= rows x N].
+ * Softmax is applied to `out` in place. */
+int sk_output_error(sk_ctx *ctx, const sk_dense *layer, const void *target, uint32_t target_rows,
+                    uint32_t rows, uint32_t loss, uint32_t act, float leaky_coeff);
+
+/* First half of GpuContext::gpu_hidden_layer_backward_pass (src/io/device/ffn_device.rs:360-436):
+ * delta of `cur` from next.d_prenorm and next's (already updated) weights. batch_stat is the
+ * batch size used for BatchNorm's 1/M (the whole batch under data parallelism). */
+int sk_hidden_error(sk_ctx *ctx, const sk_dense *cur, const sk_dense *next, uint32_t batch,
+                    uint32_t batch_stat);
+
+/* GpuContext::gpu_backward_pass (src/io/device/ffn_device.rs:234-358) with the checks of
+ * DenseBlock::backward_output (src/mlp.rs:607-642): dW, dB, sum dNorm and the in-place optimiser
+ * step. x is T [x_rows x K] (the block's forward input). */
+int sk_backward_update(sk_ctx *ctx, const sk_dense *layer, const void *x, uint32_t x_rows,
+                       uint32_t batch, const sk_optim *linear, const sk_optim *norm_opt,
+                       float learn_rate, float grad_clamp, uint32_t step);
+
+/* The two halves of sk_backward_update, for data parallelism (no counterpart in the
+ * reference, which is single-device): sk_backward_grads writes the raw batch sums
+ * dW f32 [K x N] and colsums f32 [3 x N] (dB, sum dNorm_w, sum dNorm_b; still x512) so
+ * that they can be summed across ranks; sk_apply_update divides by loss scale and
+ * batch_stat and runs the optimiser on them. */
+int sk_backward_grads(sk_ctx *ctx, const sk_dense *layer, const void *x, uint32_t x_rows,
+                      uint32_t batch, float *dw, float *colsums);
+int sk_apply_update(sk_ctx *ctx, const sk_dense *layer, const float *dw, const float *colsums,
+                    uint32_t batch_stat, const sk_optim *linear, const sk_optim *norm_opt,
+                    float learn_rate, float grad_clamp, uint32_t step);
+
+/* GpuContext::gpu_cast_t (src/io/device/util_device.rs:7-47): f32 <-> 16-bit, len elements. */
+int sk_cast(sk_ctx *ctx, const void *src, uint32_t src_dtype, void *dst, uint32_t dst_dtype, size_t len);
+/* GpuContext::gpu_broadcast (src/io/device/util_device.rs:49-78). */
+int sk_fill(sk_ctx *ctx, void *dst, uint32_t dtype, float value, size_t len);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SOKLYN_B200_H */
