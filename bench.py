@@ -1,0 +1,296 @@
+"""Benchmark of the DenseBlock / FeedForwardNetwork training step.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--config 4]
+
+Workload (default): BASELINE config 4, the wide FFN 4096->16384->4096->16384->4096 in FP16
+with FP32 masters, RMSNorm + SiLU, MSE, Adam, global batch 8192 split by rows across N
+GPUs (strong scaling). One step = forward + backward + optimiser update of every layer.
+Prints ONE JSON line (rank 0). Data are seeded synthetic tensors (soklyn_b200.configs).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "tflops": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled during the timed region (read-only query)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.idx, self.proc = device_index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.05)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [c.strip() for c in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+def timed_steps(step_fn, steps, warmup, world, device):
+    """W untimed steps, then K steps between barrier+synchronize, CUDA events, max over ranks (ms)."""
+    import torch.distributed as dist
+    for i in range(warmup):
+        step_fn(i + 1)
+    torch.cuda.synchronize(device)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        step_fn(warmup + i + 1)
+    e1.record()
+    torch.cuda.synchronize(device)
+    if world > 1:
+        dist.barrier()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return float(ms.item())
+
+
+def cpu_baseline_leg(spec, sample_rows: int):
+    """The CPU oracle (a port: the reference has no CPU path) on `sample_rows` rows of the workload, one step."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import harness as H
+    from soklyn_b200 import configs
+    small = configs.scaled(spec, batch=sample_rows)
+    w = configs.make_weights(small)
+    x, t, _ = configs.make_data(small)
+    net = H.build_oracle(small, w)
+    opt = H._oracle_optim(small)
+    t0 = time.perf_counter()
+    outs = net.forward(x, small.batch, small.use_dropout, 1)
+    net.backward(outs, t, x, small.loss, small.loss_act, opt, opt, small.batch, small.lr, 1)
+    dt = time.perf_counter() - t0
+    cores = len(os.sched_getaffinity(0))
+    return {"value": sample_rows / dt, "unit": "samples/s", "cores": cores, "kind": "port",
+            "sample": f"1 step on {sample_rows} of {spec.batch} rows (OpenMP, {cores} threads), {dt:.1f} s"}
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    import soklyn_b200 as sk
+    from soklyn_b200 import configs
+    from soklyn_b200.core import Tensor
+    from soklyn_b200.dp import DataParallelFFN
+    rank, local_rank, world = dist_env()
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    spec = configs.CONFIGS[args.config]
+    if args.batch:
+        spec = configs.scaled(spec, batch=args.batch)
+    ctx = sk.GpuContext(16, local_rank)
+    local = spec.batch // world
+    net = configs.build_network(ctx, spec, max_batch=local)
+    dp = DataParallelFFN(ctx, net, spec.batch, rank, world)
+    x, t, _ = configs.make_data(spec)
+    r0 = rank * local
+    prec = spec.prec()
+    tdt = torch.float16 if spec.precision == "f16" else torch.float32
+    x_host = torch.from_numpy(x[r0:r0 + local]).to(tdt).pin_memory()
+    t_host = torch.from_numpy(t[r0:r0 + local]).to(tdt).pin_memory()
+    xd = Tensor.from_cpu_vector(ctx, x_host, x_host.shape, prec)
+    td = Tensor.from_cpu_vector(ctx, t_host, t_host.shape, prec)
+    tc = spec.train_context()
+    lc = spec.loss_config()
+
+    def step_resident(s):
+        outs = dp.forward(xd, spec.use_dropout, s)
+        dp.backward(outs, td, xd, lc, tc, s)
+
+    out_host = torch.empty((local, spec.dims[-1]), dtype=tdt).pin_memory()
+
+    def step_e2e(s):
+        xs = Tensor.from_cpu_vector(ctx, x_host, x_host.shape, prec)
+        ts = Tensor.from_cpu_vector(ctx, t_host, t_host.shape, prec)
+        outs = dp.forward(xs, spec.use_dropout, s)
+        out_host.copy_(outs[-1].data[:local], non_blocking=True)
+        dp.backward(outs, ts, xs, lc, tc, s)
+        torch.cuda.current_stream().synchronize()   # the step's result is on the host
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = ctx.launch_count()
+    ms = timed_steps(step_resident, args.steps, args.warmup, world, device)
+    launches = ctx.launch_count() - launches0 - 0
+    clocks = sampler.stop() if rank == 0 else None
+    # per-kernel-class device times over a second, profiled pass of the same K steps
+    ctx.profile_enable(True)
+    for i in range(args.steps):
+        step_resident(args.warmup + args.steps + i + 1)
+    prof = ctx.profile_read()
+    ctx.profile_enable(False)
+    ms_e2e = timed_steps(step_e2e, args.steps, 1, world, device)
+
+    if rank == 0:
+        peaks = measured_peaks()
+        per_step = ms / args.steps
+        gemm = {k: v for k, v in prof.items() if k.startswith("gemm")}
+        top = max(gemm, key=lambda k: gemm[k][1])
+        m_local = local
+        flops = {"gemm_forward": sum(2.0 * m_local * spec.dims[i] * spec.dims[i + 1] for i in range(spec.layers)),
+                 "gemm_dw": sum(2.0 * m_local * spec.dims[i] * spec.dims[i + 1] for i in range(spec.layers)),
+                 "gemm_dx": sum(2.0 * m_local * spec.dims[i] * spec.dims[i + 1] for i in range(1, spec.layers))}
+        n_l, t_ms = gemm[top]
+        achieved = flops[top] * args.steps / (t_ms * 1e-3) / 1e12 if t_ms > 0 else 0.0
+        line = {
+            "metric": "FFN train samples/s", "value": spec.batch / (per_step * 1e-3), "unit": "samples/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": spec.precision, "data": "synthetic (seeded N(0,1) inputs/targets, Xavier-uniform weights)",
+            "config": {"workload": spec.name, "global_batch": spec.batch, "parallelism": f"dp{world}",
+                       "params": spec.params(), "l2": "working set per step is far larger than L2 (126 MB)"},
+            "tflops_per_step": spec.flops_per_step() / 1e12,
+            "tflops_achieved": spec.flops_per_step() / (per_step * 1e-3) / 1e12,
+            "e2e": {"value": spec.batch / (ms_e2e / args.steps * 1e-3), "unit": "samples/s",
+                    "h2d_bytes_per_step": (x_host.numel() + t_host.numel()) * x_host.element_size(),
+                    "d2h_bytes_per_step": out_host.numel() * out_host.element_size()},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+            "roofline": {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": peaks["tflops"],
+                         "unit": "TFLOP/s", "frac": achieved / peaks["tflops"], "traffic": None,
+                         "peak_source": peaks["source"] + " (bf16 matmul, sustained)",
+                         "launches": int(n_l), "ms_per_launch": t_ms / max(1, n_l)},
+            "kernel_ms_per_step": {k: v[1] / args.steps for k, v in prof.items()},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline_leg(spec, args.cpu_rows)
+        print(json.dumps(line), flush=True)
+    ctx.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    """The reference's own kernels (oracle/_ref: its unmodified nn_math.cu, JIT-ed from compute_75 PTX as its
+    build.rs targets) with its launch configuration and per-launch stream synchronisation, on a bounded
+    sample of the workload's batch. Falls back to the CPU port of the reference when oracle/_ref is absent."""
+    rank, local_rank, world = dist_env()
+    if rank != 0:
+        return
+    from soklyn_b200 import configs
+    spec = configs.CONFIGS[args.config]
+    rows = args.ref_rows
+    sample = configs.scaled(spec, batch=rows)
+    from oracle import ref_kernels
+    if not ref_kernels.available():
+        cb = cpu_baseline_leg(spec, args.cpu_rows)
+        line = {"impl": "reference", "metric": "FFN train samples/s", "value": cb["value"], "unit": "samples/s",
+                "n_gpus": world, "steps": 1, "warmup": 0, "ms_per_step": 1e3 * args.cpu_rows / cb["value"],
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic", "config": {"workload": spec.name, "global_batch": spec.batch},
+                "cpu_baseline": cb, "e2e": {"value": cb["value"], "unit": "samples/s", "h2d_bytes_per_step": 0,
+                                            "d2h_bytes_per_step": 0}}
+        print(json.dumps(line), flush=True)
+        return
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import harness as H
+    from soklyn_b200.core import Tensor
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    ctx = ref_kernels.RefContext(16, local_rank, sync_each_launch=True)
+    w = configs.make_weights(sample)
+    x, t, _ = configs.make_data(sample)
+    net = H.build_device(ctx, sample, w)
+    xd = Tensor.from_cpu_vector(ctx, x, x.shape, sample.prec())
+    td = Tensor.from_cpu_vector(ctx, t, t.shape, sample.prec())
+    tc, lc = sample.train_context(), sample.loss_config()
+
+    def step(s):
+        outs = net.forward(ctx, xd, rows, sample.use_dropout, s)
+        net.backward(ctx, outs, td, xd, lc, tc, s)
+
+    l0 = ctx.ref_launch_count()
+    ms = timed_steps(step, args.steps, args.warmup, 1, device)
+    per_step = ms / args.steps
+    val = rows / (per_step * 1e-3)
+    line = {"impl": "reference", "metric": "FFN train samples/s", "value": val, "unit": "samples/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": spec.precision, "data": "synthetic",
+            "config": {"workload": spec.name, "global_batch": spec.batch, "sample_rows": rows},
+            "gpu_launches": int(ctx.ref_launch_count() - l0),
+            "cpu_baseline": {"value": val, "unit": "samples/s", "cores": 1, "kind": "reference",
+                             "sample": f"the reference's own CUDA kernels (it has no CPU path) on one B200, one host "
+                                       f"thread, {rows} of {spec.batch} rows per step, synchronising after every launch"},
+            "e2e": {"value": val, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+    ctx.close()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", type=int, default=4)
+    ap.add_argument("--batch", type=int, default=0, help="override the global batch (parity/debug runs)")
+    ap.add_argument("--cpu-rows", type=int, default=16, help="rows of the batch the CPU baseline leg runs")
+    ap.add_argument("--ref-rows", type=int, default=256, help="rows of the batch the reference arm runs per step")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -102,6 +102,15 @@ const char *sk_last_error(const sk_ctx *ctx);
 /* Number of kernels this context has launched since creation (for launch accounting). */
 uint64_t sk_launch_count(const sk_ctx *ctx);
 
+/* Per-kernel-class device timing (no counterpart; the reference times phases on the host,
+ * examples/mnist_train.rs:180-195). While enabled, every launch of the classes below is
+ * bracketed by CUDA events on the context's stream; sk_profile_read waits for the stream and
+ * returns launches and total milliseconds of one class since sk_profile_enable(ctx, 1). */
+enum { SK_PROF_GEMM_FORWARD = 0, SK_PROF_GEMM_DX = 1, SK_PROF_GEMM_DW = 2, SK_PROF_NORM = 3,
+       SK_PROF_OUTPUT_ERROR = 4, SK_PROF_COLSUM = 5, SK_PROF_UPDATE = 6, SK_PROF_CLASSES = 7 };
+int sk_profile_enable(sk_ctx *ctx, int on);
+int sk_profile_read(sk_ctx *ctx, uint32_t kernel_class, uint64_t *launches, double *total_ms);
+
 /* scramble_seed (src/util/core.rs:90-94). */
 uint32_t sk_scramble_seed(uint32_t step, uint32_t tensor_id);
 

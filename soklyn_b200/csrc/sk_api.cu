@@ -1,0 +1,541 @@
+// C ABI of the DenseBlock path: context, argument checks and kernel dispatch.
+// The checks restate DenseBlock's own (Felix1G/soklyn src/mlp.rs:492-519, 548-580,
+// 607-642, 674-736, 756-821) so that a binding can forward status codes unchanged.
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "../../include/soklyn_b200.h"
+#include "sk_gemm_simt.cuh"
+#include "sk_rowwise.cuh"
+
+struct sk_ctx {
+    int device = 0;
+    uint32_t tile_dim = 16;
+    cudaStream_t stream = nullptr;
+    bool own_stream = false;
+    void *workspace = nullptr;
+    size_t workspace_bytes = 0;
+    int num_sms = 148;
+    size_t smem_optin = 0;
+    uint64_t launches = 0;
+    char err[512] = {0};
+    // optional per-class event timing
+    bool profiling = false;
+    std::vector<cudaEvent_t> ev_pool;      // pairs: [2i] start, [2i+1] stop
+    std::vector<uint32_t> ev_class;        // class of pair i
+    size_t ev_used = 0;
+};
+
+namespace {
+using namespace sk;
+
+int fail(sk_ctx *c, int code, const char *fmt, ...) {
+    if (c) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(c->err, sizeof c->err, fmt, ap);
+        va_end(ap);
+    }
+    return code;
+}
+
+int check_cuda(sk_ctx *c, cudaError_t e, const char *what) {
+    if (e == cudaSuccess) return SK_OK;
+    return fail(c, SK_ERR_DRIVER, "%s: %s", what, cudaGetErrorString(e));
+}
+
+// Brackets one launch with events when profiling is on.
+struct ProfScope {
+    sk_ctx *c;
+    size_t slot = (size_t)-1;
+    ProfScope(sk_ctx *ctx, uint32_t cls) : c(ctx) {
+        if (!c->profiling) return;
+        if (c->ev_used * 2 + 2 > c->ev_pool.size()) {
+            cudaEvent_t a, b;
+            if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) return;
+            c->ev_pool.push_back(a); c->ev_pool.push_back(b); c->ev_class.push_back(cls);
+        }
+        slot = c->ev_used++;
+        c->ev_class[slot] = cls;
+        cudaEventRecord(c->ev_pool[2 * slot], c->stream);
+    }
+    ~ProfScope() { if (slot != (size_t)-1) cudaEventRecord(c->ev_pool[2 * slot + 1], c->stream); }
+};
+
+inline bool aligned16(const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
+
+Optim make_optim(const sk_optim *o, uint32_t step) {
+    Optim r{};
+    r.kind = o->kind; r.beta1 = o->beta1; r.beta2 = o->beta2; r.epsilon = o->epsilon; r.nesterov = o->nesterov;
+    r.bc1 = 1.0f - powf(o->beta1, (float)step);
+    r.bc2 = 1.0f - powf(o->beta2, (float)step);
+    return r;
+}
+
+int check_layer(sk_ctx *c, const sk_dense *L, bool training) {
+    if (!c || !L) return SK_ERR_NULL_POINTER;
+    if (L->dtype > SK_BF16) return fail(c, SK_ERR_INVALID_CONFIGURATION, "unknown dtype %u", L->dtype);
+    if (L->K == 0 || L->N == 0) return fail(c, SK_ERR_INVALID_CONFIGURATION, "Input or output size cannot be 0.");
+    if (L->max_batch == 0) return fail(c, SK_ERR_INVALID_CONFIGURATION, "Batch size cannot be 0.");
+    if (L->norm > 3 || L->act > 7 || L->regu > 2) return fail(c, SK_ERR_INVALID_CONFIGURATION, "ordinal out of range");
+    if (L->dtype != SK_F32 && c->tile_dim != 16)
+        return fail(c, SK_ERR_HARDWARE_CONSTRAINT, "16-bit precision requires a tile dimension of 16, found %u", c->tile_dim);
+    if (!L->w || !L->b || !L->norm_w || !L->norm_b || !L->out || !L->predrop || !L->preact || !L->centered ||
+        !L->prenorm || !L->norm_rstd || !L->mask)
+        return fail(c, SK_ERR_NULL_POINTER, "forward tensor pointer is NULL");
+    if (training) {
+        if (!L->is_training) return fail(c, SK_ERR_TRAINING_MODE_REQUIRED, "block is in inference mode");
+        if (!L->grad || !L->d_prenorm || !L->d_norm_w || !L->d_norm_b || !L->dv_w || !L->dv_b || !L->dm_w || !L->dm_b ||
+            !L->dv_norm_w || !L->dv_norm_b || !L->dm_norm_w || !L->dm_norm_b)
+            return fail(c, SK_ERR_NULL_POINTER, "training tensor pointer is NULL");
+        if (L->dtype != SK_F32 && (!L->master_w || !L->master_b || !L->master_norm_w || !L->master_norm_b || !L->d_prenorm_lp))
+            return fail(c, SK_ERR_NULL_POINTER, "16-bit training needs master copies and d_prenorm_lp");
+    }
+    return SK_OK;
+}
+
+// DenseBlock::check_input_dimension (src/mlp.rs:492-519) + the batch checks of forward/backward.
+int check_batch(sk_ctx *c, const sk_dense *L, uint32_t x_rows, uint32_t batch) {
+    if (x_rows < batch) return fail(c, SK_ERR_MISMATCHED_DIMENSIONS, "input rows vs explicit batch size: expected %u, found %u", batch, x_rows);
+    if (x_rows > L->max_batch) return fail(c, SK_ERR_ALLOCATION_LIMIT, "input batches: received %u exceeds max %u", x_rows, L->max_batch);
+    if (L->act == SK_ACT_SOFTMAX) return fail(c, SK_ERR_INVALID_CONFIGURATION, "Softmax activation can only be passed into the compute_loss function.");
+    if (batch == 0) return fail(c, SK_ERR_INVALID_BATCH_SIZE, "Batch size must be more than zero.");
+    if (L->norm == SK_NORM_BATCH && batch == 1) return fail(c, SK_ERR_INVALID_BATCH_SIZE, "BatchNorm needs a batch size of more than 1.");
+    return SK_OK;
+}
+
+template <typename T> inline float *master_of(float *m, void *p) { return m ? m : reinterpret_cast<float *>(p); }
+
+// all [rows x N] tensors of a block can be accessed with 128-bit runs
+bool layer_vec_ok(const sk_dense *L) {
+    const void *ps[] = {L->b, L->norm_w, L->norm_b, L->out, L->predrop, L->preact, L->centered, L->prenorm, L->norm_rstd,
+                        L->mask, L->grad, L->d_prenorm, L->d_norm_w, L->d_norm_b, L->d_prenorm_lp, L->master_norm_w};
+    for (const void *p : ps) if (p && !aligned16(p)) return false;
+    return L->N % 8 == 0;
+}
+
+// ------------------------------------------------------------------------------------------
+template <typename T>
+int forward_impl(sk_ctx *c, const sk_dense *L, const void *x, uint32_t batch, uint32_t use_dropout, uint32_t step,
+                 uint32_t row_offset) {
+    const uint32_t seed = sk_scramble_seed(step, L->tensor_id);
+    const bool has_norm = L->norm != SK_NORM_DISABLED;
+    const bool vec = layer_vec_ok(L);
+    EpiForward<T> epi{};
+    epi.bias = L->norm != SK_NORM_BATCH ? (const T *)L->b : nullptr;
+    epi.z = (T *)(has_norm ? L->prenorm : L->preact);
+    epi.predrop = (T *)L->predrop; epi.out = (T *)L->out; epi.mask = (T *)L->mask;
+    epi.N = L->N; epi.has_norm = has_norm; epi.act = L->act; epi.use_dropout = use_dropout; epi.seed = seed;
+    epi.row_offset = row_offset; epi.leaky = L->leaky_coeff; epi.mask_coeff = L->mask_coeff; epi.vec_ok = vec;
+    int rc;
+    {
+        ProfScope ps(c, SK_PROF_GEMM_FORWARD);
+        rc = check_cuda(c, launch_gemm_simt<T, T, true, true>(c->stream, c->num_sms, (const T *)x, L->K, (const T *)L->w,
+                                                               L->N, batch, L->N, L->K, epi), "forward gemm");
+    }
+    c->launches++;
+    if (rc || !has_norm) return rc;
+    ProfScope ps(c, SK_PROF_NORM);
+    ActDrop ad{L->act, use_dropout, seed, row_offset, L->leaky_coeff, L->mask_coeff};
+    if (L->norm == SK_NORM_BATCH) {
+        norm_cols_kernel<T><<<(L->N + 31) / 32, kRowThreads, 0, c->stream>>>(
+            (const T *)L->prenorm, (const T *)L->norm_w, (const T *)L->norm_b, (T *)L->centered, (T *)L->preact,
+            (T *)L->predrop, (T *)L->out, (T *)L->mask, (T *)L->norm_rstd, batch, L->N, ad);
+    } else {
+        const size_t cache_bytes = (size_t)L->N * sizeof(float);
+        const bool cached = cache_bytes <= c->smem_optin;
+        norm_rows_kernel<T><<<batch, kRowThreads, cached ? cache_bytes : 0, c->stream>>>(
+            (const T *)L->prenorm, (const T *)L->norm_w, (const T *)L->norm_b, (T *)L->centered, (T *)L->preact,
+            (T *)L->predrop, (T *)L->out, (T *)L->mask, (T *)L->norm_rstd, L->N, L->norm, ad, vec, cached);
+    }
+    c->launches++;
+    return check_cuda(c, cudaGetLastError(), "forward norm");
+}
+
+template <typename T>
+int output_error_impl(sk_ctx *c, const sk_dense *L, const void *target, uint32_t rows, uint32_t loss, uint32_t act,
+                      float leaky) {
+    // rows below `rows` are fully overwritten; the reference zeroes d_norm_* first, which
+    // only shows in the rows beyond.
+    if (rows < L->max_batch) {
+        const size_t off = (size_t)rows * L->N, bytes = (size_t)(L->max_batch - rows) * L->N * sizeof(float);
+        cudaMemsetAsync(L->d_norm_w + off, 0, bytes, c->stream);
+        cudaMemsetAsync(L->d_norm_b + off, 0, bytes, c->stream);
+    }
+    const uint32_t warps = kRowThreads / 32;
+    ProfScope ps(c, SK_PROF_OUTPUT_ERROR);
+    output_error_kernel<T><<<(rows + warps - 1) / warps, kRowThreads, 0, c->stream>>>(
+        (T *)L->out, (const T *)L->preact, (const T *)target, master_of<T>(L->master_norm_w, L->norm_w), L->grad,
+        L->d_prenorm, L->d_norm_w, L->d_norm_b, L->dtype == SK_F32 ? nullptr : (T *)L->d_prenorm_lp,
+        (const T *)L->norm_rstd, (const T *)L->centered, (const T *)L->prenorm, rows, L->N, loss, L->norm, act, leaky);
+    c->launches++;
+    return check_cuda(c, cudaGetLastError(), "output error");
+}
+
+template <typename T>
+int hidden_error_impl(sk_ctx *c, const sk_dense *cur, const sk_dense *next, uint32_t batch, uint32_t batch_stat) {
+    if (batch < cur->max_batch) {
+        const size_t off = (size_t)batch * cur->N, bytes = (size_t)(cur->max_batch - batch) * cur->N * sizeof(float);
+        cudaMemsetAsync(cur->d_norm_w + off, 0, bytes, c->stream);
+        cudaMemsetAsync(cur->d_norm_b + off, 0, bytes, c->stream);
+    }
+    const bool f32 = cur->dtype == SK_F32;
+    EpiHidden<T> epi{};
+    epi.predrop = (const T *)cur->predrop; epi.preact = (const T *)cur->preact; epi.mask = (const T *)cur->mask;
+    epi.prenorm = (const T *)cur->prenorm; epi.centered = (const T *)cur->centered; epi.rstd = (const T *)cur->norm_rstd;
+    epi.norm_w = master_of<T>(cur->master_norm_w, cur->norm_w);
+    epi.grad = cur->grad; epi.d_prenorm = cur->d_prenorm; epi.d_norm_w = cur->d_norm_w; epi.d_norm_b = cur->d_norm_b;
+    epi.d_prenorm_lp = f32 ? nullptr : (T *)cur->d_prenorm_lp;
+    epi.N = cur->N; epi.norm = cur->norm; epi.act = cur->act; epi.leaky = cur->leaky_coeff;
+    epi.inv_n = 1.0f / (float)cur->N; epi.inv_m = 1.0f / (float)batch_stat; epi.vec_ok = layer_vec_ok(cur);
+    const uint32_t ec = next->N;
+    const T *dy = f32 ? (const T *)next->d_prenorm : (const T *)next->d_prenorm_lp;
+    const T *wn = f32 ? (const T *)master_of<T>(next->master_w, next->w) : (const T *)next->w;
+    ProfScope ps(c, SK_PROF_GEMM_DX);
+    int rc = check_cuda(c, launch_gemm_simt<T, T, true, false>(c->stream, c->num_sms, dy, ec, wn, ec, batch, cur->N, ec, epi),
+                        "hidden error gemm");
+    c->launches++;
+    return rc;
+}
+
+// Column-sum stage 1 into the workspace; returns the number of partial slabs (0 on error).
+uint32_t launch_colsum_partial(sk_ctx *c, const sk_dense *L, uint32_t batch, int *rc) {
+    const uint32_t gx = (L->N + 31) / 32;
+    uint32_t gy = (uint32_t)((4 * c->num_sms + gx - 1) / gx);
+    gy = gy < 1 ? 1 : gy;
+    const uint32_t max_gy = (batch + 7) / 8;
+    if (gy > max_gy) gy = max_gy;
+    const uint32_t rows_per_block = (batch + gy - 1) / gy;
+    gy = (batch + rows_per_block - 1) / rows_per_block;
+    const size_t need = (size_t)gy * 3 * L->N * sizeof(float);
+    if (need > c->workspace_bytes) {
+        *rc = fail(c, SK_ERR_WORKSPACE, "column sums need %zu bytes of workspace, context has %zu", need, c->workspace_bytes);
+        return 0;
+    }
+    ProfScope ps(c, SK_PROF_COLSUM);
+    colsum_partial_kernel<<<dim3(gx, gy), kRowThreads, 0, c->stream>>>(L->d_prenorm, L->d_norm_w, L->d_norm_b,
+                                                                        (float *)c->workspace, batch, L->N, rows_per_block, L->norm);
+    c->launches++;
+    *rc = check_cuda(c, cudaGetLastError(), "column sums");
+    return *rc ? 0 : gy;
+}
+
+template <typename T>
+int vector_update_launch(sk_ctx *c, const sk_dense *L, const float *partial, uint32_t nblocks, const Optim &lin,
+                         const Optim &nrm, const Hyper &hyp) {
+    ProfScope ps(c, SK_PROF_UPDATE);
+    vector_update_kernel<T><<<(L->N + 127) / 128, 128, 0, c->stream>>>(
+        partial, nblocks, L->N, (T *)L->b, master_of<T>(L->master_b, L->b), L->dv_b, L->dm_b,
+        (T *)L->norm_w, master_of<T>(L->master_norm_w, L->norm_w), L->dv_norm_w, L->dm_norm_w,
+        (T *)L->norm_b, master_of<T>(L->master_norm_b, L->norm_b), L->dv_norm_b, L->dm_norm_b,
+        L->norm != SK_NORM_BATCH, L->norm, lin, nrm, hyp);
+    c->launches++;
+    return check_cuda(c, cudaGetLastError(), "bias / norm parameter step");
+}
+
+template <typename T>
+int backward_update_impl(sk_ctx *c, const sk_dense *L, const void *x, uint32_t batch, const sk_optim *lin_,
+                         const sk_optim *nrm_, float lr, float clamp, uint32_t step) {
+    const Optim lin = make_optim(lin_, step), nrm = make_optim(nrm_, step);
+    const Hyper hyp{lr, clamp, 1.0f / (float)batch, L->regu, L->regu_coeff};
+    int rc = SK_OK;
+    const uint32_t nblocks = launch_colsum_partial(c, L, batch, &rc);
+    if (rc) return rc;
+    if ((rc = vector_update_launch<T>(c, L, (const float *)c->workspace, nblocks, lin, nrm, hyp))) return rc;
+    const bool f32 = L->dtype == SK_F32;
+    EpiWeightUpdate<T> epi{};
+    epi.w = (T *)L->w; epi.master = master_of<T>(L->master_w, L->w); epi.dv = L->dv_w; epi.dm = L->dm_w;
+    epi.N = L->N; epi.opt = lin; epi.hyp = hyp;
+    epi.vec_ok = L->N % 8 == 0 && aligned16(L->w) && aligned16(epi.master) && aligned16(L->dv_w) && aligned16(L->dm_w);
+    ProfScope ps(c, SK_PROF_GEMM_DW);
+    if (f32)
+        rc = check_cuda(c, launch_gemm_simt<T, float, false, true>(c->stream, c->num_sms, (const T *)x, L->K, L->d_prenorm,
+                                                                    L->N, L->K, L->N, batch, epi), "weight gradient gemm");
+    else
+        rc = check_cuda(c, launch_gemm_simt<T, T, false, true>(c->stream, c->num_sms, (const T *)x, L->K,
+                                                                (const T *)L->d_prenorm_lp, L->N, L->K, L->N, batch, epi),
+                        "weight gradient gemm");
+    c->launches++;
+    return rc;
+}
+
+template <typename T>
+int backward_grads_impl(sk_ctx *c, const sk_dense *L, const void *x, uint32_t batch, float *dw, float *colsums) {
+    int rc = SK_OK;
+    const uint32_t nblocks = launch_colsum_partial(c, L, batch, &rc);
+    if (rc) return rc;
+    colsum_final_kernel<<<(3 * L->N + 255) / 256, 256, 0, c->stream>>>((const float *)c->workspace, colsums, L->N, nblocks);
+    c->launches++;
+    if ((rc = check_cuda(c, cudaGetLastError(), "column sums (final)"))) return rc;
+    EpiStoreF32 epi{dw, L->N, L->N % 8 == 0 && aligned16(dw)};
+    ProfScope ps(c, SK_PROF_GEMM_DW);
+    if (L->dtype == SK_F32)
+        rc = check_cuda(c, launch_gemm_simt<T, float, false, true>(c->stream, c->num_sms, (const T *)x, L->K, L->d_prenorm,
+                                                                    L->N, L->K, L->N, batch, epi), "weight gradient gemm");
+    else
+        rc = check_cuda(c, launch_gemm_simt<T, T, false, true>(c->stream, c->num_sms, (const T *)x, L->K,
+                                                                (const T *)L->d_prenorm_lp, L->N, L->K, L->N, batch, epi),
+                        "weight gradient gemm");
+    c->launches++;
+    return rc;
+}
+
+template <typename T>
+int apply_update_impl(sk_ctx *c, const sk_dense *L, const float *dw, const float *colsums, uint32_t batch_stat,
+                      const sk_optim *lin_, const sk_optim *nrm_, float lr, float clamp, uint32_t step) {
+    const Optim lin = make_optim(lin_, step), nrm = make_optim(nrm_, step);
+    const Hyper hyp{lr, clamp, 1.0f / (float)batch_stat, L->regu, L->regu_coeff};
+    int rc = vector_update_launch<T>(c, L, colsums, 1, lin, nrm, hyp);
+    if (rc) return rc;
+    const size_t len = (size_t)L->K * L->N;
+    float *master = master_of<T>(L->master_w, L->w);
+    const bool vec = len % 4 == 0 && aligned16(dw) && aligned16(L->w) && aligned16(master) && aligned16(L->dv_w) && aligned16(L->dm_w);
+    size_t blocks = (len / 4 + kRowThreads - 1) / kRowThreads;
+    const size_t cap = (size_t)c->num_sms * 8;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    ProfScope ps(c, SK_PROF_UPDATE);
+    weight_update_kernel<T><<<(uint32_t)blocks, kRowThreads, 0, c->stream>>>(dw, (T *)L->w, master, L->dv_w, L->dm_w, len, lin, hyp, vec);
+    c->launches++;
+    return check_cuda(c, cudaGetLastError(), "weight step");
+}
+
+#define SK_DISPATCH(dtype, fn, ...)                                        \
+    ((dtype) == SK_F32 ? fn<float>(__VA_ARGS__)                            \
+     : (dtype) == SK_F16 ? fn<__half>(__VA_ARGS__) : fn<__nv_bfloat16>(__VA_ARGS__))
+
+} // namespace
+
+extern "C" {
+
+int sk_ctx_create(int device, uint32_t tile_dim, void *stream, size_t workspace_bytes, sk_ctx **out) {
+    if (!out) return SK_ERR_NULL_POINTER;
+    *out = nullptr;
+    if (tile_dim == 0 || tile_dim > 32) return SK_ERR_INVALID_CONFIGURATION;
+    if (cudaSetDevice(device) != cudaSuccess) return SK_ERR_DRIVER;
+    sk_ctx *c = new (std::nothrow) sk_ctx();
+    if (!c) return SK_ERR_DRIVER;
+    c->device = device;
+    c->tile_dim = tile_dim;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) { delete c; return SK_ERR_DRIVER; }
+    c->num_sms = prop.multiProcessorCount;
+    // dynamic shared memory the row kernels may use for their row cache (static part left free)
+    c->smem_optin = prop.sharedMemPerBlockOptin > 8192 ? prop.sharedMemPerBlockOptin - 8192 : 0;
+    if (stream) {
+        c->stream = reinterpret_cast<cudaStream_t>(stream);
+    } else {
+        if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) { delete c; return SK_ERR_DRIVER; }
+        c->own_stream = true;
+    }
+    const int optin = (int)c->smem_optin;
+    cudaFuncSetAttribute(sk::norm_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
+    cudaFuncSetAttribute(sk::norm_rows_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
+    cudaFuncSetAttribute(sk::norm_rows_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
+    if (workspace_bytes == 0) workspace_bytes = (size_t)64 << 20;
+    if (cudaMalloc(&c->workspace, workspace_bytes) != cudaSuccess) {
+        if (c->own_stream) cudaStreamDestroy(c->stream);
+        delete c;
+        return SK_ERR_DRIVER;
+    }
+    c->workspace_bytes = workspace_bytes;
+    *out = c;
+    return SK_OK;
+}
+
+void sk_ctx_destroy(sk_ctx *c) {
+    if (!c) return;
+    cudaSetDevice(c->device);
+    cudaStreamSynchronize(c->stream);
+    if (c->workspace) cudaFree(c->workspace);
+    for (cudaEvent_t e : c->ev_pool) cudaEventDestroy(e);
+    if (c->own_stream) cudaStreamDestroy(c->stream);
+    delete c;
+}
+
+int sk_ctx_set_stream(sk_ctx *c, void *stream) {
+    if (!c) return SK_ERR_NULL_POINTER;
+    if (c->own_stream) { cudaStreamSynchronize(c->stream); cudaStreamDestroy(c->stream); c->own_stream = false; }
+    c->stream = reinterpret_cast<cudaStream_t>(stream);
+    return SK_OK;
+}
+
+int sk_ctx_reserve(sk_ctx *c, size_t workspace_bytes) {
+    if (!c) return SK_ERR_NULL_POINTER;
+    if (workspace_bytes <= c->workspace_bytes) return SK_OK;
+    cudaSetDevice(c->device);
+    cudaStreamSynchronize(c->stream);
+    void *p = nullptr;
+    int rc = check_cuda(c, cudaMalloc(&p, workspace_bytes), "workspace allocation");
+    if (rc) return rc;
+    cudaFree(c->workspace);
+    c->workspace = p;
+    c->workspace_bytes = workspace_bytes;
+    return SK_OK;
+}
+
+int sk_sync(sk_ctx *c) {
+    if (!c) return SK_ERR_NULL_POINTER;
+    return check_cuda(c, cudaStreamSynchronize(c->stream), "stream synchronize");
+}
+
+const char *sk_status_string(int s) {
+    switch (s) {
+    case SK_OK: return "ok";
+    case SK_ERR_DRIVER: return "Driver error";
+    case SK_ERR_MISMATCHED_DIMENSIONS: return "Dimension mismatch";
+    case SK_ERR_ALLOCATION_LIMIT: return "Allocation limit exceeded";
+    case SK_ERR_INVALID_CONFIGURATION: return "Invalid network configuration";
+    case SK_ERR_INVALID_BATCH_SIZE: return "Batch size constraint violation";
+    case SK_ERR_TRAINING_MODE_REQUIRED: return "Action requires the network to be in training mode";
+    case SK_ERR_HARDWARE_CONSTRAINT: return "Hardware acceleration constraint violation";
+    case SK_ERR_UNSUPPORTED_CAST: return "Unsupported precision cast operation";
+    case SK_ERR_NULL_POINTER: return "Required pointer is NULL";
+    case SK_ERR_WORKSPACE: return "Scratch workspace too small";
+    case SK_ERR_DEVICE_TIMEOUT: return "Device-side wait timed out";
+    default: return "unknown status";
+    }
+}
+
+const char *sk_last_error(const sk_ctx *c) { return c ? c->err : ""; }
+uint64_t sk_launch_count(const sk_ctx *c) { return c ? c->launches : 0; }
+
+int sk_profile_enable(sk_ctx *c, int on) {
+    if (!c) return SK_ERR_NULL_POINTER;
+    c->profiling = on != 0;
+    if (on) c->ev_used = 0;
+    return SK_OK;
+}
+
+int sk_profile_read(sk_ctx *c, uint32_t cls, uint64_t *launches, double *total_ms) {
+    if (!c || !launches || !total_ms) return SK_ERR_NULL_POINTER;
+    if (cls >= SK_PROF_CLASSES) return fail(c, SK_ERR_INVALID_CONFIGURATION, "unknown kernel class %u", cls);
+    int rc = check_cuda(c, cudaStreamSynchronize(c->stream), "stream synchronize");
+    if (rc) return rc;
+    *launches = 0;
+    *total_ms = 0.0;
+    for (size_t i = 0; i < c->ev_used; ++i) {
+        if (c->ev_class[i] != cls) continue;
+        float ms = 0.0f;
+        if (cudaEventElapsedTime(&ms, c->ev_pool[2 * i], c->ev_pool[2 * i + 1]) == cudaSuccess) {
+            *total_ms += ms;
+            ++*launches;
+        }
+    }
+    return SK_OK;
+}
+
+uint32_t sk_scramble_seed(uint32_t step, uint32_t id) {
+    uint32_t h = step * 1103515245u + id;
+    h = (h ^ (h >> 16)) * 1103515245u;
+    return h ^ (h >> 15);
+}
+
+int sk_dense_forward(sk_ctx *c, const sk_dense *L, const void *x, uint32_t x_rows, uint32_t batch,
+                     uint32_t use_dropout, uint32_t step, uint32_t row_offset) {
+    int rc = check_layer(c, L, false);
+    if (rc) return rc;
+    if (!x) return fail(c, SK_ERR_NULL_POINTER, "input pointer is NULL");
+    if ((rc = check_batch(c, L, x_rows, batch))) return rc;
+    return SK_DISPATCH(L->dtype, forward_impl, c, L, x, batch, use_dropout, step, row_offset);
+}
+
+int sk_output_error(sk_ctx *c, const sk_dense *L, const void *target, uint32_t target_rows, uint32_t rows,
+                    uint32_t loss, uint32_t act, float leaky) {
+    int rc = check_layer(c, L, true);
+    if (rc) return rc;
+    if (!target) return fail(c, SK_ERR_NULL_POINTER, "target pointer is NULL");
+    if (target_rows > L->max_batch) return fail(c, SK_ERR_ALLOCATION_LIMIT, "target batches: received %u exceeds max %u", target_rows, L->max_batch);
+    if (rows == 0 || rows > L->max_batch || rows > target_rows)
+        return fail(c, SK_ERR_MISMATCHED_DIMENSIONS, "rows %u must be within target rows %u and max batch %u", rows, target_rows, L->max_batch);
+    if (loss > 2 || act > 7) return fail(c, SK_ERR_INVALID_CONFIGURATION, "ordinal out of range");
+    if (loss == SK_LOSS_MSE && act == SK_ACT_SOFTMAX)
+        return fail(c, SK_ERR_INVALID_CONFIGURATION, "Mean Squared Loss does not support the Softmax activation function.");
+    if (loss == SK_LOSS_CROSS_ENTROPY && act != SK_ACT_SOFTMAX)
+        return fail(c, SK_ERR_INVALID_CONFIGURATION, "Cross-Entropy Loss only supports the Softmax activation function.");
+    if (loss == SK_LOSS_BINARY_CROSS_ENTROPY && act != SK_ACT_SIGMOID)
+        return fail(c, SK_ERR_INVALID_CONFIGURATION, "Binary Cross-Entropy only supports the Sigmoid activation function.");
+    return SK_DISPATCH(L->dtype, output_error_impl, c, L, target, rows, loss, act, leaky);
+}
+
+int sk_hidden_error(sk_ctx *c, const sk_dense *cur, const sk_dense *next, uint32_t batch, uint32_t batch_stat) {
+    int rc = check_layer(c, cur, true);
+    if (rc) return rc;
+    if ((rc = check_layer(c, next, true))) return rc;
+    if (cur->dtype != next->dtype) return fail(c, SK_ERR_INVALID_CONFIGURATION, "adjacent blocks differ in precision");
+    if (next->K != cur->N)
+        return fail(c, SK_ERR_MISMATCHED_DIMENSIONS, "next layer rows vs current cols: expected %u, found %u", cur->N, next->K);
+    if (next->max_batch < batch)
+        return fail(c, SK_ERR_MISMATCHED_DIMENSIONS, "next layer gradient rows %u below batch %u", next->max_batch, batch);
+    if (cur->act == SK_ACT_SOFTMAX) return fail(c, SK_ERR_INVALID_CONFIGURATION, "Softmax activation can only be passed into the compute_loss function.");
+    if (batch == 0 || batch_stat == 0) return fail(c, SK_ERR_INVALID_BATCH_SIZE, "Batch size must be more than zero.");
+    if (batch > cur->max_batch) return fail(c, SK_ERR_ALLOCATION_LIMIT, "batch %u exceeds max %u", batch, cur->max_batch);
+    if (cur->norm == SK_NORM_BATCH && batch_stat == 1) return fail(c, SK_ERR_INVALID_BATCH_SIZE, "BatchNorm needs a batch size of more than 1.");
+    return SK_DISPATCH(cur->dtype, hidden_error_impl, c, cur, next, batch, batch_stat);
+}
+
+int sk_backward_update(sk_ctx *c, const sk_dense *L, const void *x, uint32_t x_rows, uint32_t batch,
+                       const sk_optim *lin, const sk_optim *nrm, float lr, float clamp, uint32_t step) {
+    int rc = check_layer(c, L, true);
+    if (rc) return rc;
+    if (!x || !lin || !nrm) return fail(c, SK_ERR_NULL_POINTER, "input or optimiser pointer is NULL");
+    if ((rc = check_batch(c, L, x_rows, batch))) return rc;
+    if (lin->kind > 1 || nrm->kind > 1) return fail(c, SK_ERR_INVALID_CONFIGURATION, "optimiser ordinal out of range");
+    return SK_DISPATCH(L->dtype, backward_update_impl, c, L, x, batch, lin, nrm, lr, clamp, step);
+}
+
+int sk_backward_grads(sk_ctx *c, const sk_dense *L, const void *x, uint32_t x_rows, uint32_t batch, float *dw,
+                      float *colsums) {
+    int rc = check_layer(c, L, true);
+    if (rc) return rc;
+    if (!x || !dw || !colsums) return fail(c, SK_ERR_NULL_POINTER, "input or output pointer is NULL");
+    if ((rc = check_batch(c, L, x_rows, batch))) return rc;
+    return SK_DISPATCH(L->dtype, backward_grads_impl, c, L, x, batch, dw, colsums);
+}
+
+int sk_apply_update(sk_ctx *c, const sk_dense *L, const float *dw, const float *colsums, uint32_t batch_stat,
+                    const sk_optim *lin, const sk_optim *nrm, float lr, float clamp, uint32_t step) {
+    int rc = check_layer(c, L, true);
+    if (rc) return rc;
+    if (!dw || !colsums || !lin || !nrm) return fail(c, SK_ERR_NULL_POINTER, "gradient or optimiser pointer is NULL");
+    if (batch_stat == 0) return fail(c, SK_ERR_INVALID_BATCH_SIZE, "Batch size must be more than zero.");
+    if (lin->kind > 1 || nrm->kind > 1) return fail(c, SK_ERR_INVALID_CONFIGURATION, "optimiser ordinal out of range");
+    return SK_DISPATCH(L->dtype, apply_update_impl, c, L, dw, colsums, batch_stat, lin, nrm, lr, clamp, step);
+}
+
+int sk_cast(sk_ctx *c, const void *src, uint32_t sd, void *dst, uint32_t dd, size_t len) {
+    if (!c || !src || !dst) return SK_ERR_NULL_POINTER;
+    if (len == 0) return SK_OK;
+    size_t blocks = (len + 1023) / 1024;
+    const size_t cap = (size_t)c->num_sms * 16;
+    if (blocks > cap) blocks = cap;
+    const uint32_t g = (uint32_t)blocks;
+    if (sd == SK_F32 && dd == SK_F16) sk::cast_kernel<float, __half><<<g, 256, 0, c->stream>>>((const float *)src, (__half *)dst, len);
+    else if (sd == SK_F16 && dd == SK_F32) sk::cast_kernel<__half, float><<<g, 256, 0, c->stream>>>((const __half *)src, (float *)dst, len);
+    else if (sd == SK_F32 && dd == SK_BF16) sk::cast_kernel<float, __nv_bfloat16><<<g, 256, 0, c->stream>>>((const float *)src, (__nv_bfloat16 *)dst, len);
+    else if (sd == SK_BF16 && dd == SK_F32) sk::cast_kernel<__nv_bfloat16, float><<<g, 256, 0, c->stream>>>((const __nv_bfloat16 *)src, (float *)dst, len);
+    else return fail(c, SK_ERR_UNSUPPORTED_CAST, "cannot convert dtype %u to %u", sd, dd);
+    c->launches++;
+    return check_cuda(c, cudaGetLastError(), "cast");
+}
+
+int sk_fill(sk_ctx *c, void *dst, uint32_t dtype, float value, size_t len) {
+    if (!c || !dst) return SK_ERR_NULL_POINTER;
+    if (len == 0) return SK_OK;
+    size_t blocks = (len + 1023) / 1024;
+    const size_t cap = (size_t)c->num_sms * 16;
+    if (blocks > cap) blocks = cap;
+    const uint32_t g = (uint32_t)blocks;
+    if (dtype == SK_F32) sk::fill_kernel<float><<<g, 256, 0, c->stream>>>((float *)dst, value, len);
+    else if (dtype == SK_F16) sk::fill_kernel<__half><<<g, 256, 0, c->stream>>>((__half *)dst, value, len);
+    else if (dtype == SK_BF16) sk::fill_kernel<__nv_bfloat16><<<g, 256, 0, c->stream>>>((__nv_bfloat16 *)dst, value, len);
+    else return fail(c, SK_ERR_INVALID_CONFIGURATION, "unknown dtype %u", dtype);
+    c->launches++;
+    return check_cuda(c, cudaGetLastError(), "fill");
+}
+
+} // extern "C"

@@ -1,0 +1,164 @@
+// FFMA-tiled GEMM for the f32 path and for 16-bit shapes the tensor-core kernel cannot
+// take (leading dimensions that are not multiples of 16 bytes, tiny matrices).
+//
+//   C[m, n] = sum_k A(m, k) * B(k, n),   one fused-multiply-add chain per output in
+//   increasing k (the summation order of the reference's dev_gemm, src/cuda/kernel/math.cu:8-50).
+//
+// A and B are read through (contiguous-direction, leading-dimension) pairs so that the
+// three products of a DenseBlock run straight from the row-major tensors:
+//   forward  Y = X.W        A k-contiguous (X[m*K+k]),   B n-contiguous (W[k*N+n])
+//   dX       S = dY.W^T     A k-contiguous (dY[m*E+k]),  B k-contiguous (W[n*E+k])
+//   dW       G = X^T.dY     A m-contiguous (X[k*K+m]),   B n-contiguous (dY[k*N+n])
+// Tiles are staged in shared memory as [k][m] and [k][n] f32 panels with 128-bit
+// coalesced global loads, register prefetch of the next panel, and a TM x TN register
+// block per thread. The epilogue functor gets runs of TN consecutive columns.
+#pragma once
+
+#include "sk_epilogue.cuh"
+
+namespace sk {
+
+constexpr int kSimtThreads = 256;
+constexpr int kSimtBK = 16;
+
+// Load E contiguous elements starting at p (valid: how many of them exist) as f32.
+template <typename T, int E>
+__device__ __forceinline__ void load_guarded(const T *p, int valid, bool vec_ok, float (&out)[E]) {
+    if (vec_ok && valid >= E) {
+        load_run<T, E>(p, true, out);
+    } else {
+#pragma unroll
+        for (int i = 0; i < E; ++i) out[i] = i < valid ? to_f32(p[i]) : 0.0f;
+    }
+}
+
+template <typename TA, typename TB, bool A_KCONTIG, bool B_NCONTIG, int BM, int BN, int TM, int TN, class Epi>
+__global__ void __launch_bounds__(kSimtThreads)
+gemm_simt_kernel(const TA *__restrict__ A, const TB *__restrict__ B, uint32_t M, uint32_t N, uint32_t K,
+                 size_t lda, size_t ldb, bool a_vec, bool b_vec, Epi epi) {
+    constexpr int BK = kSimtBK;
+    constexpr int EA = BM * BK / kSimtThreads; // elements of A per thread per panel
+    constexpr int EB = BN * BK / kSimtThreads;
+    static_assert((BM / TM) * (BN / TN) == kSimtThreads, "thread block must cover the tile");
+    static_assert(EA >= 1 && EB >= 1 && BK % EA == 0 && BK % EB == 0, "panel split");
+    constexpr int PAD = 4;
+    __shared__ __align__(16) float As[BK][BM + PAD];
+    __shared__ __align__(16) float Bs[BK][BN + PAD];
+
+    const int t = threadIdx.x;
+    const uint32_t m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int tx = t % (BN / TN), ty = t / (BN / TN);
+
+    // per-thread source coordinates inside a panel
+    int a_mn, a_k, b_mn, b_k;
+    if (A_KCONTIG) { a_mn = t / (BK / EA); a_k = (t % (BK / EA)) * EA; }
+    else           { a_k = t / (BM / EA); a_mn = (t % (BM / EA)) * EA; }
+    if (B_NCONTIG) { b_k = t / (BN / EB); b_mn = (t % (BN / EB)) * EB; }
+    else           { b_mn = t / (BK / EB); b_k = (t % (BK / EB)) * EB; }
+
+    float ra[EA], rb[EB];
+    auto fetch = [&](uint32_t k0) {
+        if (A_KCONTIG) {
+            const uint32_t m = m0 + a_mn, k = k0 + a_k;
+            const int valid = m < M ? (int)K - (int)k : 0;
+            load_guarded<TA, EA>(A + (size_t)m * lda + k, valid, a_vec, ra);
+        } else {
+            const uint32_t m = m0 + a_mn, k = k0 + a_k;
+            const int valid = k < K ? (int)M - (int)m : 0;
+            load_guarded<TA, EA>(A + (size_t)k * lda + m, valid, a_vec, ra);
+        }
+        if (B_NCONTIG) {
+            const uint32_t n = n0 + b_mn, k = k0 + b_k;
+            const int valid = k < K ? (int)N - (int)n : 0;
+            load_guarded<TB, EB>(B + (size_t)k * ldb + n, valid, b_vec, rb);
+        } else {
+            const uint32_t n = n0 + b_mn, k = k0 + b_k;
+            const int valid = n < N ? (int)K - (int)k : 0;
+            load_guarded<TB, EB>(B + (size_t)n * ldb + k, valid, b_vec, rb);
+        }
+    };
+    auto stage = [&]() {
+        if (A_KCONTIG) {
+#pragma unroll
+            for (int i = 0; i < EA; ++i) As[a_k + i][a_mn] = ra[i];
+        } else {
+#pragma unroll
+            for (int i = 0; i < EA; ++i) As[a_k][a_mn + i] = ra[i];
+        }
+        if (B_NCONTIG) {
+#pragma unroll
+            for (int i = 0; i < EB; ++i) Bs[b_k][b_mn + i] = rb[i];
+        } else {
+#pragma unroll
+            for (int i = 0; i < EB; ++i) Bs[b_k + i][b_mn] = rb[i];
+        }
+    };
+
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+
+    fetch(0);
+    for (uint32_t k0 = 0; k0 < K; k0 += BK) {
+        stage();
+        __syncthreads();
+        if (k0 + BK < K) fetch(k0 + BK);
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            float a[TM], b[TN];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) a[i] = As[kk][ty * TM + i];
+#pragma unroll
+            for (int j = 0; j < TN; ++j) b[j] = Bs[kk][tx * TN + j];
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+
+    const uint32_t col0 = n0 + tx * TN;
+    if (col0 >= N) return;
+    const uint32_t ncols = min((uint32_t)TN, N - col0);
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const uint32_t row = m0 + ty * TM + i;
+        if (row < M) epi.template run<TN>(row, col0, acc[i], ncols);
+    }
+}
+
+struct GemmOperand {
+    const void *ptr;
+    size_t ld;       // leading dimension in elements
+    bool contig_k;   // true: (mn, k) -> ptr[mn*ld + k]; false: ptr[k*ld + mn]
+};
+
+// Host-side launcher: picks the tile so that small problems still spread over the SMs.
+template <typename TA, typename TB, bool A_KCONTIG, bool B_NCONTIG, class Epi>
+cudaError_t launch_gemm_simt(cudaStream_t stream, int num_sms, const TA *A, size_t lda, const TB *B, size_t ldb,
+                             uint32_t M, uint32_t N, uint32_t K, const Epi &epi) {
+    auto aligned = [](const void *p, size_t ld, size_t es) {
+        return (reinterpret_cast<uintptr_t>(p) % 16 == 0) && ((ld * es) % 16 == 0);
+    };
+    const bool a_vec = aligned(A, lda, sizeof(TA)), b_vec = aligned(B, ldb, sizeof(TB));
+    auto ctas = [&](uint32_t bm, uint32_t bn) { return (size_t)((M + bm - 1) / bm) * ((N + bn - 1) / bn); };
+    if (ctas(128, 128) >= (size_t)num_sms) {
+        dim3 grid((N + 127) / 128, (M + 127) / 128);
+        gemm_simt_kernel<TA, TB, A_KCONTIG, B_NCONTIG, 128, 128, 8, 8, Epi>
+            <<<grid, kSimtThreads, 0, stream>>>(A, B, M, N, K, lda, ldb, a_vec, b_vec, epi);
+    } else if (ctas(64, 64) >= (size_t)num_sms) {
+        dim3 grid((N + 63) / 64, (M + 63) / 64);
+        gemm_simt_kernel<TA, TB, A_KCONTIG, B_NCONTIG, 64, 64, 4, 4, Epi>
+            <<<grid, kSimtThreads, 0, stream>>>(A, B, M, N, K, lda, ldb, a_vec, b_vec, epi);
+    } else {
+        dim3 grid((N + 31) / 32, (M + 31) / 32);
+        gemm_simt_kernel<TA, TB, A_KCONTIG, B_NCONTIG, 32, 32, 2, 2, Epi>
+            <<<grid, kSimtThreads, 0, stream>>>(A, B, M, N, K, lda, ldb, a_vec, b_vec, epi);
+    }
+    return cudaGetLastError();
+}
+
+} // namespace sk

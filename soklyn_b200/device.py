@@ -1,0 +1,152 @@
+"""GpuContext of the host mirror (reference: src/io/device.rs and src/io/device/{ffn,util}_device.rs).
+
+Each `gpu_*` method is one call into the C ABI (include/soklyn_b200.h), in place of the
+reference's kernel-by-name launches. Calls are ordered on this context's stream, which is
+torch's current stream at construction unless one is given; unlike the reference the
+methods do not block the host, `synchronize()` does.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _native, log
+from ._native import SkDense, SkOptim
+from .core import SK_DTYPE, Tensor
+from .function import Activation, LossFunc, Normalisation, Optimiser, Precision
+
+
+def _optim(o: Optimiser) -> SkOptim:
+    b1, b2, eps, nest = o.kernel_args()
+    return SkOptim(o.ordinal(), b1, b2, eps, nest)
+
+
+class GpuContext:
+    def __init__(self, tile_dim: int = 16, ordinal: int = 0, stream: "torch.cuda.Stream | None" = None,
+                 workspace_bytes: int = 0):
+        if not torch.cuda.is_available():
+            raise log.DriverError("Failed to create CUDA context: no CUDA device (there is no CPU path)")
+        self.lib = _native.lib()
+        self.device = torch.device("cuda", ordinal)
+        self.tile_dim = tile_dim
+        torch.cuda.set_device(self.device)
+        self.stream = stream if stream is not None else torch.cuda.current_stream(self.device)
+        handle = C.c_void_p()
+        rc = self.lib.sk_ctx_create(ordinal, tile_dim, C.c_void_p(self.stream.cuda_stream), workspace_bytes,
+                                    C.byref(handle))
+        if rc != 0:
+            raise log.DriverError(f"sk_ctx_create failed with status {rc} ({_native.STATUS.get(rc)})")
+        self.handle = handle
+
+    @staticmethod
+    def new(tile_dim: int) -> "GpuContext":
+        return GpuContext(tile_dim, 0)
+
+    @staticmethod
+    def with_device_index(ordinal: int, tile_dim: int) -> "GpuContext":
+        return GpuContext(tile_dim, ordinal)
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.lib.sk_ctx_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- helpers --
+    def _check(self, rc: int):
+        if rc != 0:
+            log.raise_status(rc, self.lib.sk_last_error(self.handle).decode())
+
+    def set_stream(self, stream: "torch.cuda.Stream"):
+        self.stream = stream
+        self._check(self.lib.sk_ctx_set_stream(self.handle, C.c_void_p(stream.cuda_stream)))
+
+    def reserve(self, workspace_bytes: int):
+        self._check(self.lib.sk_ctx_reserve(self.handle, workspace_bytes))
+
+    def synchronize(self):
+        self._check(self.lib.sk_sync(self.handle))
+
+    def launch_count(self) -> int:
+        return int(self.lib.sk_launch_count(self.handle))
+
+    PROFILE_CLASSES = ("gemm_forward", "gemm_dx", "gemm_dw", "norm", "output_error", "colsum", "update")
+
+    def profile_enable(self, on: bool = True):
+        self._check(self.lib.sk_profile_enable(self.handle, int(on)))
+
+    def profile_read(self) -> dict:
+        """{class: (launches, total_ms)} since profile_enable(True); waits for the stream."""
+        out = {}
+        for i, name in enumerate(self.PROFILE_CLASSES):
+            n, ms = C.c_uint64(), C.c_double()
+            self._check(self.lib.sk_profile_read(self.handle, i, C.byref(n), C.byref(ms)))
+            out[name] = (n.value, ms.value)
+        return out
+
+    def get_tile_dim(self) -> int:
+        return self.tile_dim
+
+    def download(self, tensor: Tensor):
+        return tensor.download(self)
+
+    def check_tile_dim(self, precision: Precision):
+        """src/io/device.rs:248-258"""
+        if precision != Precision.FP32 and self.tile_dim != 16:
+            raise log.HardwareConstraintViolation(precision, 16, self.tile_dim)
+
+    # -- src/io/device/util_device.rs:7-78 --
+    def gpu_cast_t(self, src: Tensor, dst: Tensor):
+        if src.len() != dst.len():
+            raise log.MismatchedDimensions("GPU precision cast source vs destination buffer sizes", dst.len(), src.len())
+        if (src.precision == Precision.FP32) == (dst.precision == Precision.FP32):
+            raise log.UnsupportedTypeCast(src.precision, dst.precision)
+        self._check(self.lib.sk_cast(self.handle, src.ptr(), SK_DTYPE[src.precision], dst.ptr(),
+                                     SK_DTYPE[dst.precision], src.len()))
+
+    def gpu_broadcast(self, dst: Tensor, value: float):
+        self._check(self.lib.sk_fill(self.handle, dst.ptr(), SK_DTYPE[dst.precision], value, dst.len()))
+
+    # -- src/io/device/ffn_device.rs --
+    def gpu_forward_pass(self, layer, input: Tensor, batch_size: int, use_dropout: bool, step: int,
+                         row_offset: int = 0):
+        self.check_tile_dim(layer.precision)
+        self._check(self.lib.sk_dense_forward(self.handle, C.byref(layer.desc()), input.ptr(), input.rows(),
+                                              batch_size, int(use_dropout), step & 0xFFFFFFFF, row_offset))
+
+    def gpu_compute_output_layer_error(self, layer, target: Tensor, err_mode: LossFunc, activation: Activation):
+        rows = layer.get_outputs().rows()
+        self._check(self.lib.sk_output_error(self.handle, C.byref(layer.desc()), target.ptr(), target.rows(), rows,
+                                             err_mode.value, activation.ordinal(), activation.coeff))
+
+    def gpu_backward_pass(self, layer, input: Tensor, train_ctx, step: int):
+        lin, nrm = _optim(train_ctx.optimiser), _optim(train_ctx.norm_optimiser)
+        self._check(self.lib.sk_backward_update(self.handle, C.byref(layer.desc()), input.ptr(), input.rows(),
+                                                train_ctx.batch_size, C.byref(lin), C.byref(nrm),
+                                                train_ctx.learn_rate, train_ctx.grad_clamp, step & 0xFFFFFFFF))
+
+    def gpu_hidden_layer_error(self, cur, nxt, batch_size: int, batch_stat: int | None = None):
+        self.check_tile_dim(cur.precision)
+        self._check(self.lib.sk_hidden_error(self.handle, C.byref(cur.desc()), C.byref(nxt.desc()), batch_size,
+                                             batch_size if batch_stat is None else batch_stat))
+
+    def gpu_hidden_layer_backward_pass(self, cur, nxt, input: Tensor, activation, train_ctx, step: int):
+        self.gpu_hidden_layer_error(cur, nxt, train_ctx.batch_size)
+        self.gpu_backward_pass(cur, input, train_ctx, step)
+
+    # -- data-parallel halves (no counterpart in the reference) --
+    def gpu_backward_grads(self, layer, input: Tensor, batch_size: int, dw: torch.Tensor, colsums: torch.Tensor):
+        self._check(self.lib.sk_backward_grads(self.handle, C.byref(layer.desc()), input.ptr(), input.rows(),
+                                               batch_size, dw.data_ptr(), colsums.data_ptr()))
+
+    def gpu_apply_update(self, layer, dw: torch.Tensor, colsums: torch.Tensor, batch_stat: int, train_ctx, step: int):
+        lin, nrm = _optim(train_ctx.optimiser), _optim(train_ctx.norm_optimiser)
+        self._check(self.lib.sk_apply_update(self.handle, C.byref(layer.desc()), dw.data_ptr(), colsums.data_ptr(),
+                                             batch_stat, C.byref(lin), C.byref(nrm), train_ctx.learn_rate,
+                                             train_ctx.grad_clamp, step & 0xFFFFFFFF))
