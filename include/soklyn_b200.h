@@ -86,9 +86,12 @@ typedef struct {
 
 /* GpuContext::with_device_index (src/io/device.rs:164-183). tile_dim is kept for API
  * compatibility: 16-bit modes still require 16 (src/io/device.rs:248-258), the kernels
- * ignore it. `stream` is a cudaStream_t to run on, or NULL for a stream the context
- * creates. workspace_bytes of scratch are allocated here (0 = default 64 MiB). */
-int sk_ctx_create(int device, uint32_t tile_dim, void *stream, size_t workspace_bytes, sk_ctx **out);
+ * ignore it. With create_stream != 0 the context creates (and owns) a non-blocking stream,
+ * as the reference's GpuContext does; otherwise calls are ordered on the cudaStream_t
+ * `stream`, where NULL is the legacy default stream. workspace_bytes of scratch are
+ * allocated here (0 = default 64 MiB). */
+int sk_ctx_create(int device, uint32_t tile_dim, void *stream, int create_stream, size_t workspace_bytes,
+                  sk_ctx **out);
 void sk_ctx_destroy(sk_ctx *ctx);
 /* Replace the stream later calls are ordered on (no counterpart; the reference owns one stream). */
 int sk_ctx_set_stream(sk_ctx *ctx, void *stream);

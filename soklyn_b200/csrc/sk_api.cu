@@ -312,7 +312,7 @@ int apply_update_impl(sk_ctx *c, const sk_dense *L, const float *dw, const float
 
 extern "C" {
 
-int sk_ctx_create(int device, uint32_t tile_dim, void *stream, size_t workspace_bytes, sk_ctx **out) {
+int sk_ctx_create(int device, uint32_t tile_dim, void *stream, int create_stream, size_t workspace_bytes, sk_ctx **out) {
     if (!out) return SK_ERR_NULL_POINTER;
     *out = nullptr;
     if (tile_dim == 0 || tile_dim > 32) return SK_ERR_INVALID_CONFIGURATION;
@@ -326,7 +326,7 @@ int sk_ctx_create(int device, uint32_t tile_dim, void *stream, size_t workspace_
     c->num_sms = prop.multiProcessorCount;
     // dynamic shared memory the row kernels may use for their row cache (static part left free)
     c->smem_optin = prop.sharedMemPerBlockOptin > 8192 ? prop.sharedMemPerBlockOptin - 8192 : 0;
-    if (stream) {
+    if (!create_stream) {
         c->stream = reinterpret_cast<cudaStream_t>(stream);
     } else {
         if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) { delete c; return SK_ERR_DRIVER; }

@@ -33,7 +33,7 @@ class GpuContext:
         torch.cuda.set_device(self.device)
         self.stream = stream if stream is not None else torch.cuda.current_stream(self.device)
         handle = C.c_void_p()
-        rc = self.lib.sk_ctx_create(ordinal, tile_dim, C.c_void_p(self.stream.cuda_stream), workspace_bytes,
+        rc = self.lib.sk_ctx_create(ordinal, tile_dim, C.c_void_p(self.stream.cuda_stream), 0, workspace_bytes,
                                     C.byref(handle))
         if rc != 0:
             raise log.DriverError(f"sk_ctx_create failed with status {rc} ({_native.STATUS.get(rc)})")

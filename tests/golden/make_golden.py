@@ -26,7 +26,7 @@ def golden_specs():
     odd = configs.NetSpec(9, "odd_shapes", (37, 50, 21, 7), ("batch", "rms", "disabled"),
                           ("tanh", "leaky:0.1", "identity"), (0.0, 0.3, 0.0), "f32", "mse", "sigmoid", "adam", 1e-3, 19,
                           "he_normal", "normal", "normal", True)
-    bce = configs.NetSpec(8, "bce_head", (48, 32, 16), ("layer", "disabled"), ("sigmoid", "identity"), (0.0, 0.0),
+    bce = configs.NetSpec(8, "bce_head", (48, 32, 48), ("layer", "disabled"), ("sigmoid", "identity"), (0.0, 0.0),
                           "f32", "bce", "sigmoid", "sgd", 0.05, 24, "xavier_uniform", "u8", "input")
     return [(CONFIGS[1], 2), (scaled(CONFIGS[2], precision="f32", name="autoencoder_f32"), 2), (small3, 2), (small4, 2),
             (odd, 2), (bce, 2)]

@@ -105,9 +105,22 @@ def device_state(ctx, layer) -> dict:
     return out
 
 
-def compare_states(ctx, spec, dev_net, oracle_net, tol, skip=()):
-    """Max norm-wise relative error per tensor name over all layers; asserts each <= tol."""
+PARAMS = ("w", "b", "norm_w", "norm_b")
+
+
+def compare_states(ctx, spec, dev_net, oracle_net, tol, skip=(), steps=1):
+    """Max norm-wise relative error per tensor name over all layers; asserts each <= tol.
+
+    Parameters updated by Adam get their own rule. Adam's step is lr*m/(sqrt(v)+eps); at
+    step 1 that is lr*g/(|g|+eps), about lr*sign(g): an element whose gradient lies within
+    rounding noise of zero can land anywhere in [-lr, +lr] whichever (correct) summation
+    order produced it, and the reference's own GPU kernels differ from a CPU run in the same
+    way. So for Adam the gradient is checked through the first moment dm = (1-b1)*g at `tol`,
+    and the parameters by how far they moved in units of lr: in f32 every element within
+    0.1*lr per step; in 16-bit 99% of the elements within 0.1*lr and all within 2.5*lr per step.
+    """
     worst = {}
+    lr_max = max(lr_schedule(spec, max(steps, 1)))
     for i, (dl, ol) in enumerate(zip(dev_net.get_layers(), oracle_net.layers)):
         ds, os_ = device_state(ctx, dl), ol.state()
         rows = spec.batch
@@ -124,5 +137,13 @@ def compare_states(ctx, spec, dev_net, oracle_net, tol, skip=()):
                     continue
             e = relerr(got, ref)
             worst[name] = max(worst.get(name, 0.0), e)
+            if name in PARAMS and spec.optimiser == "adam" and e > tol:
+                diff = np.abs(got.astype(np.float64) - ref.astype(np.float64)) / lr_max
+                if tol <= 1e-3:
+                    assert diff.max() <= 0.1 * steps, f"layer {i} {name}: moved {diff.max():.3f} lr from the oracle"
+                else:
+                    assert (diff > 0.1 * steps).mean() <= 0.01 and diff.max() <= 2.5 * steps, \
+                        f"layer {i} {name}: {100 * (diff > 0.1 * steps).mean():.2f}% beyond 0.1 lr, max {diff.max():.2f} lr"
+                continue
             assert e <= tol, f"layer {i} tensor {name}: relative error {e:.3e} > {tol:.1e}"
     return worst

@@ -43,7 +43,7 @@ def test_host_only_entry_points():
 
 def test_null_arguments_are_rejected_without_a_device():
     lib = _native.lib()
-    assert lib.sk_ctx_create(0, 16, None, 0, None) == 9          # NULL out pointer
+    assert lib.sk_ctx_create(0, 16, None, 0, 0, None) == 9          # NULL out pointer
     assert lib.sk_dense_forward(None, None, None, 0, 0, 0, 0, 0) == 9
     assert lib.sk_sync(None) == 9
 
