@@ -5,7 +5,7 @@
 
 Inputs and weights are regenerated from seeds by soklyn_b200.configs, so only outputs are
 stored: every tensor of every layer after `steps` training steps, sampled with a fixed
-stride (at most ~512 values per tensor) plus its f64 sum and absolute sum.
+stride (at most ~160 values per tensor) plus its f64 sum and absolute sum.
 """
 import os
 import sys
@@ -34,7 +34,7 @@ def golden_specs():
 
 def sample(a: np.ndarray) -> np.ndarray:
     flat = np.asarray(a, np.float32).reshape(-1)
-    stride = max(1, flat.size // 512)
+    stride = max(1, flat.size // 160)
     return np.concatenate([flat[::stride], np.array([flat.astype(np.float64).sum(), np.abs(flat.astype(np.float64)).sum()],
                                                     np.float64).astype(np.float32)])
 
