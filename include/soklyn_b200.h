@@ -35,7 +35,8 @@ enum {
     SK_ERR_UNSUPPORTED_CAST = 8,       /* Error::UnsupportedTypeCast */
     SK_ERR_NULL_POINTER = 9,           /* no counterpart: a required pointer is NULL */
     SK_ERR_WORKSPACE = 10,             /* no counterpart: scratch workspace too small */
-    SK_ERR_DEVICE_TIMEOUT = 11         /* no counterpart: a bounded device-side wait gave up */
+    SK_ERR_DEVICE_TIMEOUT = 11,        /* no counterpart: a bounded device-side wait gave up */
+    SK_ERR_STATIC_LIMIT = 12           /* no counterpart: size beyond the built-in scratch of sk_column_sums_static */
 };
 
 enum { SK_F32 = 0, SK_F16 = 1, SK_BF16 = 2 };
@@ -154,6 +155,20 @@ int sk_backward_grads(sk_ctx *ctx, const sk_dense *layer, const void *x, uint32_
 int sk_apply_update(sk_ctx *ctx, const sk_dense *layer, const float *dw, const float *colsums,
                     uint32_t batch_stat, const sk_optim *linear, const sk_optim *norm_opt,
                     float learn_rate, float grad_clamp, uint32_t step);
+
+/* No counterpart in the reference. Column sums over the batch of d_prenorm, d_norm_w and
+ * d_norm_b, written to colsums f32 [3 x N] exactly as sk_backward_grads writes them, but
+ * without a context and without allocating: for callers that are not allowed to allocate
+ * device memory (their framework owns the whole device heap, or they only hold raw pointers
+ * and a stream and so cannot create an sk_ctx, whose creation allocates). The partial sums
+ * live in a 3 MiB array built into the library (present on every GPU that loads it), which
+ * limits N to 262144 columns: beyond that the call returns SK_ERR_STATIC_LIMIT. Calls share
+ * that array, so calls that overlap on the GPU race and must be serialised by the caller.
+ * The first call on a device resolves the array's address; make it before any stream capture.
+ * `stream` is a cudaStream_t (NULL = legacy default stream); norm selects which sums are
+ * taken (0: dB only, 1: + d_norm_w, 2/3: + d_norm_b), unused inputs may be NULL. */
+int sk_column_sums_static(void *stream, const float *d_prenorm, const float *d_norm_w,
+                          const float *d_norm_b, float *colsums, uint32_t batch, uint32_t N, uint32_t norm);
 
 /* GpuContext::gpu_cast_t (src/io/device/util_device.rs:7-47): f32 <-> 16-bit, len elements. */
 int sk_cast(sk_ctx *ctx, const void *src, uint32_t src_dtype, void *dst, uint32_t dst_dtype, size_t len);

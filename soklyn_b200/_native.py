@@ -25,7 +25,7 @@ STATUS = {
     0: "ok", 1: "DriverError", 2: "MismatchedDimensions", 3: "AllocationLimitExceeded",
     4: "InvalidConfiguration", 5: "InvalidBatchSize", 6: "TrainingModeRequired",
     7: "HardwareConstraintViolation", 8: "UnsupportedTypeCast", 9: "NullPointer",
-    10: "WorkspaceTooSmall", 11: "DeviceTimeout",
+    10: "WorkspaceTooSmall", 11: "DeviceTimeout", 12: "StaticScratchLimit",
 }
 
 
@@ -111,6 +111,8 @@ _SIGS = {
                                     C.c_void_p, C.c_void_p]),
     "sk_apply_update": (C.c_int, [C.c_void_p, C.POINTER(SkDense), C.c_void_p, C.c_void_p, C.c_uint32,
                                   C.POINTER(SkOptim), C.POINTER(SkOptim), C.c_float, C.c_float, C.c_uint32]),
+    "sk_column_sums_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32,
+                                        C.c_uint32, C.c_uint32]),
     "sk_cast": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_size_t]),
     "sk_fill": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_float, C.c_size_t]),
 }

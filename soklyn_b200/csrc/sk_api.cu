@@ -397,6 +397,7 @@ const char *sk_status_string(int s) {
     case SK_ERR_NULL_POINTER: return "Required pointer is NULL";
     case SK_ERR_WORKSPACE: return "Scratch workspace too small";
     case SK_ERR_DEVICE_TIMEOUT: return "Device-side wait timed out";
+    case SK_ERR_STATIC_LIMIT: return "Size exceeds the built-in scratch array (N may not exceed 262144 columns)";
     default: return "unknown status";
     }
 }
