@@ -96,9 +96,15 @@ int sk_ctx_create(int device, uint32_t tile_dim, void *stream, int create_stream
 void sk_ctx_destroy(sk_ctx *ctx);
 /* Replace the stream later calls are ordered on (no counterpart; the reference owns one stream). */
 int sk_ctx_set_stream(sk_ctx *ctx, void *stream);
+/* Context options (no counterpart). SK_OPTION_GEMM_ENGINE: 0 = automatic (tcgen05 tensor-core
+ * kernel for 16-bit operands whose row pitches are multiples of 16 bytes, FFMA kernel
+ * otherwise), 1 = FFMA kernel only. */
+enum { SK_OPTION_GEMM_ENGINE = 0 };
+int sk_ctx_set_option(sk_ctx *ctx, uint32_t option, uint32_t value);
 /* Grow the scratch workspace; never called implicitly. */
 int sk_ctx_reserve(sk_ctx *ctx, size_t workspace_bytes);
-/* CudaStream::synchronize as called after every launch in src/io/device/ffn_device.rs:75,110,136. */
+/* CudaStream::synchronize as called after every launch in src/io/device/ffn_device.rs:75,110,136.
+ * Also reports SK_ERR_DEVICE_TIMEOUT if a tensor-core kernel abandoned a bounded wait. */
 int sk_sync(sk_ctx *ctx);
 /* Text for a status code, and the detail of the last failure on this context. */
 const char *sk_status_string(int status);

@@ -92,6 +92,7 @@ _SIGS = {
     "sk_ctx_create": (C.c_int, [C.c_int, C.c_uint32, C.c_void_p, C.c_int, C.c_size_t, C.POINTER(C.c_void_p)]),
     "sk_ctx_destroy": (None, [C.c_void_p]),
     "sk_ctx_set_stream": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "sk_ctx_set_option": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint32]),
     "sk_ctx_reserve": (C.c_int, [C.c_void_p, C.c_size_t]),
     "sk_sync": (C.c_int, [C.c_void_p]),
     "sk_status_string": (C.c_char_p, [C.c_int]),

@@ -6,10 +6,15 @@
 #include <cstdio>
 #include <cstring>
 #include <new>
+#include <type_traits>
 #include <vector>
 
 #include "../../include/soklyn_b200.h"
+#include <map>
+#include <tuple>
+
 #include "sk_gemm_simt.cuh"
+#include "sk_gemm_tc.cuh"
 #include "sk_rowwise.cuh"
 
 struct sk_ctx {
@@ -23,6 +28,13 @@ struct sk_ctx {
     size_t smem_optin = 0;
     uint64_t launches = 0;
     char err[512] = {0};
+    // tensor-core path
+    int cc_major = 0;
+    uint32_t gemm_engine = 0;              // 0 auto, 1 FFMA only
+    int *tc_err = nullptr;                 // device word a tcgen05 kernel sets when a bounded wait gives up
+    void *encode_tiled = nullptr;          // cuTensorMapEncodeTiled, resolved through the runtime
+    std::map<std::tuple<const void *, uint64_t, uint64_t, uint64_t, uint32_t, uint32_t>, CUtensorMap> tmaps;
+    uint64_t tc_launches = 0;
     // optional per-class event timing
     bool profiling = false;
     std::vector<cudaEvent_t> ev_pool;      // pairs: [2i] start, [2i+1] stop
@@ -65,6 +77,86 @@ struct ProfScope {
     }
     ~ProfScope() { if (slot != (size_t)-1) cudaEventRecord(c->ev_pool[2 * slot + 1], c->stream); }
 };
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// 2-D TMA descriptor over a row-major 16-bit matrix: `inner` contiguous elements per row, `outer`
+// rows `ld` elements apart, fetched in boxes of 64 x box_outer with the 128-byte swizzle.
+const CUtensorMap *get_tmap(sk_ctx *c, const void *ptr, uint32_t dtype, uint64_t inner, uint64_t outer, uint64_t ld,
+                            uint32_t box_outer) {
+    auto key = std::make_tuple(ptr, inner, outer, ld, box_outer, dtype);
+    auto it = c->tmaps.find(key);
+    if (it != c->tmaps.end()) return &it->second;
+    if (c->tmaps.size() > 512) c->tmaps.clear();
+    CUtensorMap m;
+    const cuuint64_t gdim[2] = {inner, outer};
+    const cuuint64_t gstride[1] = {ld * 2};
+    const cuuint32_t box[2] = {64, box_outer};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = reinterpret_cast<EncodeTiledFn>(c->encode_tiled)(
+        &m, dtype == SK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+        const_cast<void *>(ptr), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return nullptr;
+    return &c->tmaps.emplace(key, m).first->second;
+}
+
+// Can the tensor-core kernel take these operands? (16-byte aligned bases, row pitches that are
+// multiples of 16 bytes, a Blackwell device, and the engine not forced to FFMA)
+bool tc_eligible(const sk_ctx *c, uint32_t dtype, const void *a, size_t lda, const void *b, size_t ldb) {
+    if (dtype == SK_F32 || c->gemm_engine == 1 || c->cc_major != 10 || !c->encode_tiled || !c->tc_err) return false;
+    auto ok = [](const void *p, size_t ld) { return reinterpret_cast<uintptr_t>(p) % 16 == 0 && ld % 8 == 0; };
+    return ok(a, lda) && ok(b, ldb);
+}
+
+template <typename T, bool A_MN, bool B_MN, int BN, class Epi>
+cudaError_t launch_tc_bn(sk_ctx *c, const CUtensorMap *ta, const CUtensorMap *tb, uint32_t M, uint32_t N, uint32_t K,
+                         const Epi &epi) {
+    using S = TcShape<BN>;
+    static bool attr_set = false;
+    auto kernel = gemm_tc_kernel<A_MN, B_MN, BN, Epi>;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    const uint32_t tiles = ((M + kTcBM - 1) / kTcBM) * ((N + BN - 1) / BN);
+    const uint32_t grid = tiles < (uint32_t)c->num_sms ? tiles : (uint32_t)c->num_sms;
+    const uint32_t idesc = tc::make_instr_desc(std::is_same<T, __nv_bfloat16>::value ? 1u : 0u, A_MN, B_MN, kTcBM, BN);
+    kernel<<<grid, kTcThreads, S::kSmemBytes, c->stream>>>(*ta, *tb, M, N, K, idesc, epi, c->tc_err);
+    c->tc_launches++;
+    return cudaGetLastError();
+}
+
+// C[M x N] = A.B on the tensor cores. A_MN / B_MN: operand contiguous along M / N (else along K).
+template <typename T, bool A_MN, bool B_MN, class Epi>
+cudaError_t launch_gemm_tc(sk_ctx *c, uint32_t dtype, const T *A, size_t lda, const T *B, size_t ldb, uint32_t M,
+                           uint32_t N, uint32_t K, const Epi &epi) {
+    auto cost = [&](uint32_t bn) {
+        const uint64_t tiles = (uint64_t)((M + kTcBM - 1) / kTcBM) * ((N + bn - 1) / bn);
+        return ((tiles + c->num_sms - 1) / c->num_sms) * bn;
+    };
+    const bool wide = N > 128 && cost(256) <= cost(128);
+    const uint32_t bn = wide ? 256 : 128;
+    const CUtensorMap *ta = A_MN ? get_tmap(c, A, dtype, M, K, lda, 64) : get_tmap(c, A, dtype, K, M, lda, kTcBM);
+    const CUtensorMap *tb = B_MN ? get_tmap(c, B, dtype, N, K, ldb, 64) : get_tmap(c, B, dtype, K, N, ldb, bn);
+    if (!ta || !tb) return cudaErrorInvalidValue;
+    return wide ? launch_tc_bn<T, A_MN, B_MN, 256, Epi>(c, ta, tb, M, N, K, epi)
+                : launch_tc_bn<T, A_MN, B_MN, 128, Epi>(c, ta, tb, M, N, K, epi);
+}
+
+// Engine choice for one product of the DenseBlock path.
+template <typename TA, typename TB, bool A_KCONTIG, bool B_NCONTIG, class Epi>
+cudaError_t run_gemm(sk_ctx *c, uint32_t dtype, const TA *A, size_t lda, const TB *B, size_t ldb, uint32_t M, uint32_t N,
+                     uint32_t K, const Epi &epi) {
+    if constexpr (std::is_same<TA, TB>::value && !std::is_same<TA, float>::value) {
+        if (tc_eligible(c, dtype, A, lda, B, ldb))
+            return launch_gemm_tc<TA, !A_KCONTIG, B_NCONTIG, Epi>(c, dtype, A, lda, B, ldb, M, N, K, epi);
+    }
+    return launch_gemm_simt<TA, TB, A_KCONTIG, B_NCONTIG, Epi>(c->stream, c->num_sms, A, lda, B, ldb, M, N, K, epi);
+}
 
 inline bool aligned16(const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
 
@@ -134,7 +226,7 @@ int forward_impl(sk_ctx *c, const sk_dense *L, const void *x, uint32_t batch, ui
     int rc;
     {
         ProfScope ps(c, SK_PROF_GEMM_FORWARD);
-        rc = check_cuda(c, launch_gemm_simt<T, T, true, true>(c->stream, c->num_sms, (const T *)x, L->K, (const T *)L->w,
+        rc = check_cuda(c, run_gemm<T, T, true, true>(c, L->dtype, (const T *)x, L->K, (const T *)L->w,
                                                                L->N, batch, L->N, L->K, epi), "forward gemm");
     }
     c->launches++;
@@ -196,7 +288,7 @@ int hidden_error_impl(sk_ctx *c, const sk_dense *cur, const sk_dense *next, uint
     const T *dy = f32 ? (const T *)next->d_prenorm : (const T *)next->d_prenorm_lp;
     const T *wn = f32 ? (const T *)master_of<T>(next->master_w, next->w) : (const T *)next->w;
     ProfScope ps(c, SK_PROF_GEMM_DX);
-    int rc = check_cuda(c, launch_gemm_simt<T, T, true, false>(c->stream, c->num_sms, dy, ec, wn, ec, batch, cur->N, ec, epi),
+    int rc = check_cuda(c, run_gemm<T, T, true, false>(c, cur->dtype, dy, ec, wn, ec, batch, cur->N, ec, epi),
                         "hidden error gemm");
     c->launches++;
     return rc;
@@ -253,10 +345,10 @@ int backward_update_impl(sk_ctx *c, const sk_dense *L, const void *x, uint32_t b
     epi.vec_ok = L->N % 8 == 0 && aligned16(L->w) && aligned16(epi.master) && aligned16(L->dv_w) && aligned16(L->dm_w);
     ProfScope ps(c, SK_PROF_GEMM_DW);
     if (f32)
-        rc = check_cuda(c, launch_gemm_simt<T, float, false, true>(c->stream, c->num_sms, (const T *)x, L->K, L->d_prenorm,
+        rc = check_cuda(c, run_gemm<T, float, false, true>(c, L->dtype, (const T *)x, L->K, L->d_prenorm,
                                                                     L->N, L->K, L->N, batch, epi), "weight gradient gemm");
     else
-        rc = check_cuda(c, launch_gemm_simt<T, T, false, true>(c->stream, c->num_sms, (const T *)x, L->K,
+        rc = check_cuda(c, run_gemm<T, T, false, true>(c, L->dtype, (const T *)x, L->K,
                                                                 (const T *)L->d_prenorm_lp, L->N, L->K, L->N, batch, epi),
                         "weight gradient gemm");
     c->launches++;
@@ -274,10 +366,10 @@ int backward_grads_impl(sk_ctx *c, const sk_dense *L, const void *x, uint32_t ba
     EpiStoreF32 epi{dw, L->N, L->N % 8 == 0 && aligned16(dw)};
     ProfScope ps(c, SK_PROF_GEMM_DW);
     if (L->dtype == SK_F32)
-        rc = check_cuda(c, launch_gemm_simt<T, float, false, true>(c->stream, c->num_sms, (const T *)x, L->K, L->d_prenorm,
+        rc = check_cuda(c, run_gemm<T, float, false, true>(c, L->dtype, (const T *)x, L->K, L->d_prenorm,
                                                                     L->N, L->K, L->N, batch, epi), "weight gradient gemm");
     else
-        rc = check_cuda(c, launch_gemm_simt<T, T, false, true>(c->stream, c->num_sms, (const T *)x, L->K,
+        rc = check_cuda(c, run_gemm<T, T, false, true>(c, L->dtype, (const T *)x, L->K,
                                                                 (const T *)L->d_prenorm_lp, L->N, L->K, L->N, batch, epi),
                         "weight gradient gemm");
     c->launches++;
@@ -336,6 +428,16 @@ int sk_ctx_create(int device, uint32_t tile_dim, void *stream, int create_stream
     cudaFuncSetAttribute(sk::norm_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
     cudaFuncSetAttribute(sk::norm_rows_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
     cudaFuncSetAttribute(sk::norm_rows_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
+    c->cc_major = prop.major;
+    {
+        cudaDriverEntryPointQueryResult q;
+        void *fn = nullptr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            c->encode_tiled = fn;
+        if (cudaMalloc(&c->tc_err, sizeof(int)) == cudaSuccess) cudaMemset(c->tc_err, 0, sizeof(int));
+        else c->tc_err = nullptr;
+    }
     if (workspace_bytes == 0) workspace_bytes = (size_t)64 << 20;
     if (cudaMalloc(&c->workspace, workspace_bytes) != cudaSuccess) {
         if (c->own_stream) cudaStreamDestroy(c->stream);
@@ -352,6 +454,7 @@ void sk_ctx_destroy(sk_ctx *c) {
     cudaSetDevice(c->device);
     cudaStreamSynchronize(c->stream);
     if (c->workspace) cudaFree(c->workspace);
+    if (c->tc_err) cudaFree(c->tc_err);
     for (cudaEvent_t e : c->ev_pool) cudaEventDestroy(e);
     if (c->own_stream) cudaStreamDestroy(c->stream);
     delete c;
@@ -380,7 +483,21 @@ int sk_ctx_reserve(sk_ctx *c, size_t workspace_bytes) {
 
 int sk_sync(sk_ctx *c) {
     if (!c) return SK_ERR_NULL_POINTER;
-    return check_cuda(c, cudaStreamSynchronize(c->stream), "stream synchronize");
+    int rc = check_cuda(c, cudaStreamSynchronize(c->stream), "stream synchronize");
+    if (rc || !c->tc_err || c->tc_launches == 0) return rc;
+    int flag = 0;
+    if ((rc = check_cuda(c, cudaMemcpy(&flag, c->tc_err, sizeof(int), cudaMemcpyDeviceToHost), "error flag read"))) return rc;
+    if (flag != 0) {
+        cudaMemset(c->tc_err, 0, sizeof(int));
+        return fail(c, SK_ERR_DEVICE_TIMEOUT, "a tensor-core GEMM gave up waiting on a barrier (role %d: 1 loader, 2 MMA issuer, 3 epilogue)", flag);
+    }
+    return SK_OK;
+}
+
+int sk_ctx_set_option(sk_ctx *c, uint32_t option, uint32_t value) {
+    if (!c) return SK_ERR_NULL_POINTER;
+    if (option == SK_OPTION_GEMM_ENGINE && value <= 1) { c->gemm_engine = value; return SK_OK; }
+    return fail(c, SK_ERR_INVALID_CONFIGURATION, "unknown option %u / value %u", option, value);
 }
 
 const char *sk_status_string(int s) {

@@ -1,0 +1,184 @@
+// Tensor-core GEMM for the 16-bit DenseBlock path on sm_100a.
+//
+//   C[M x N] = A . B, f16 or bf16 operands, f32 accumulation in tensor memory (TMEM).
+//
+// One persistent CTA per SM walks output tiles of 128 x BN. Warp 0 streams operand panels
+// (64 deep in K) from global memory into a ring of shared-memory stages with TMA tile loads
+// (128-byte swizzle); one thread of warp 1 issues tcgen05.mma instructions (M=128, N=BN, K=16)
+// that read the stages through shared-memory descriptors and accumulate into one of two TMEM
+// accumulator buffers; eight epilogue warps drain the other buffer with tcgen05.ld, pass each
+// 32 x 32 block through shared memory so that global accesses run along rows, and apply the
+// fused epilogue functor (sk_epilogue.cuh). Mainloop and epilogue of consecutive tiles overlap.
+//
+// Both operand layouts come straight from the row-major tensors, no transposed copies:
+//   K-major  operand: element (mn, k) at ptr[mn * ld + k]  -> one TMA box {64 k, rows}
+//   MN-major operand: element (mn, k) at ptr[k * ld + mn]  -> boxes {64 mn, 64 k}, 8 KiB apart
+// so forward (X K-major, W MN-major), dX (dY, W both K-major) and dW (X, dY both MN-major)
+// use the same kernel. Out-of-range parts of a box are zero-filled by TMA; the epilogue
+// clips rows and columns. Every barrier wait is bounded; on a timeout the kernel records an
+// error code and leaves.
+#pragma once
+
+#include "sk_epilogue.cuh"
+#include "sk_tc_ptx.cuh"
+
+namespace sk {
+
+constexpr int kTcBM = 128;          // tile rows = UMMA M
+constexpr int kTcBK = 64;           // K depth of one stage: 64 x 2 B = one 128-byte swizzle row
+constexpr int kTcEpiWarps = 8;
+constexpr int kTcThreads = (2 + kTcEpiWarps) * 32;
+constexpr int kTcABytes = kTcBM * kTcBK * 2;
+
+template <int BN> struct TcShape {
+    static constexpr int kBBytes = BN * kTcBK * 2;
+    static constexpr int kStageBytes = kTcABytes + kBBytes;
+    static constexpr int kStages = BN == 256 ? 4 : 6;
+    static constexpr int kTmemCols = 2 * BN;                       // two accumulator buffers
+    static constexpr int kEpiBufBytes = kTcEpiWarps * 32 * 33 * 4;
+    static constexpr int kBarBytes = (2 * kStages + 4) * 8 + 16;
+    static constexpr int kSmemBytes = 1024 /*alignment slack*/ + kStages * kStageBytes + kEpiBufBytes + kBarBytes;
+};
+
+enum : int { kTcErrProducer = 1, kTcErrMma = 2, kTcErrEpilogue = 3 };
+
+template <bool A_MN, bool B_MN, int BN, class Epi>
+__global__ void __launch_bounds__(kTcThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               uint32_t M, uint32_t N, uint32_t K, uint32_t idesc, Epi epi, int *err_flag) {
+    using S = TcShape<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *stages = smem;
+    float *epi_buf = reinterpret_cast<float *>(smem + S::kStages * S::kStageBytes);
+    uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + S::kStages * S::kStageBytes + S::kEpiBufBytes);
+    uint64_t *empty_bar = full_bar + S::kStages;
+    uint64_t *tmem_full = empty_bar + S::kStages;
+    uint64_t *tmem_empty = tmem_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t tiles_m = (M + kTcBM - 1) / kTcBM, tiles_n = (N + BN - 1) / BN;
+    const uint32_t num_tiles = tiles_m * tiles_n;
+    const uint32_t num_kb = (K + kTcBK - 1) / kTcBK;
+
+    if (warp == 0 && lane == 0) {
+        tc::prefetch_tensormap(&tmap_a);
+        tc::prefetch_tensormap(&tmap_b);
+        for (int s = 0; s < S::kStages; ++s) { tc::mbar_init(&full_bar[s], 1); tc::mbar_init(&empty_bar[s], 1); }
+        for (int b = 0; b < 2; ++b) { tc::mbar_init(&tmem_full[b], 1); tc::mbar_init(&tmem_empty[b], kTcEpiWarps * 32); }
+        tc::fence_barrier_init();
+    }
+    if (warp == 1) {
+        tc::tmem_alloc(tmem_slot, S::kTmemCols);
+        tc::tmem_relinquish();
+    }
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    tc::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int32_t m0 = (tile % tiles_m) * kTcBM, n0 = (tile / tiles_m) * BN;
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    if (!tc::mbar_wait(&empty_bar[stage], phase ^ 1)) { ok = false; break; }
+                    tc::mbar_arrive_expect_tx(&full_bar[stage], S::kStageBytes);
+                    uint8_t *sa = stages + stage * S::kStageBytes, *sb = sa + kTcABytes;
+                    const int32_t k0 = kb * kTcBK;
+                    if (A_MN) {
+#pragma unroll
+                        for (int j = 0; j < kTcBM / 64; ++j) tc::tma_load_2d(sa + j * 8192, &tmap_a, &full_bar[stage], m0 + j * 64, k0);
+                    } else {
+                        tc::tma_load_2d(sa, &tmap_a, &full_bar[stage], k0, m0);
+                    }
+                    if (B_MN) {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j) tc::tma_load_2d(sb + j * 8192, &tmap_b, &full_bar[stage], n0 + j * 64, k0);
+                    } else {
+                        tc::tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, n0);
+                    }
+                    if (++stage == S::kStages) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) atomicCAS(err_flag, 0, kTcErrProducer);
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                if (!tc::mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) { ok = false; break; }
+                tc::tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    if (!tc::mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
+                    tc::tc_fence_after_sync();
+                    const uint32_t sa = tc::smem_u32(stages + stage * S::kStageBytes), sb = sa + kTcABytes;
+#pragma unroll
+                    for (int j = 0; j < kTcBK / 16; ++j) {
+                        const uint64_t da = A_MN ? tc::make_smem_desc(sa + j * 2048, 8192, 1024)
+                                                 : tc::make_smem_desc(sa + j * 32, 16, 1024);
+                        const uint64_t db = B_MN ? tc::make_smem_desc(sb + j * 2048, 8192, 1024)
+                                                 : tc::make_smem_desc(sb + j * 32, 16, 1024);
+                        tc::umma_f16(d_tmem, da, db, idesc, kb > 0 || j > 0);
+                    }
+                    tc::umma_commit(&empty_bar[stage]);      // stage reusable once these MMAs have read it
+                    if (++stage == S::kStages) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                tc::umma_commit(&tmem_full[acc]);            // accumulator complete
+                if ((acc ^= 1) == 0) acc_phase ^= 1;
+            }
+            if (!ok) atomicCAS(err_flag, 0, kTcErrMma);
+        }
+    } else {
+        // ---------------- epilogue ----------------
+        const uint32_t ew = warp - 2;                 // 0..7
+        const uint32_t quarter = warp & 3;            // TMEM lanes this warp may read: 32*quarter ..
+        const uint32_t half = ew >> 2;                // which half of the tile's columns
+        float *buf = epi_buf + ew * (32 * 33);
+        uint32_t acc = 0, acc_phase = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            const uint32_t m0 = (tile % tiles_m) * kTcBM, n0 = (tile / tiles_m) * BN;
+            if (!tc::mbar_wait(&tmem_full[acc], acc_phase)) { ok = false; break; }
+            tc::tc_fence_after_sync();
+#pragma unroll 1
+            for (uint32_t c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32) {
+                if (n0 + c0 >= N) break;              // uniform per warp
+                float v[32];
+                tc::tmem_ld_32x32(tmem_base + ((quarter * 32) << 16) + acc * BN + c0, v);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) buf[lane * 33 + j] = v[j];
+                __syncwarp();
+#pragma unroll
+                for (int pass = 0; pass < 4; ++pass) {
+                    const uint32_t rr = pass * 8 + (lane >> 2), cc = (lane & 3) * 8;
+                    float r[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) r[j] = buf[rr * 33 + cc + j];
+                    const uint32_t row = m0 + quarter * 32 + rr, col = n0 + c0 + cc;
+                    if (row < M && col < N) epi.template run<8>(row, col, r, min(8u, N - col));
+                }
+                __syncwarp();
+            }
+            tc::tc_fence_before_sync();
+            tc::mbar_arrive(&tmem_empty[acc]);
+            if ((acc ^= 1) == 0) acc_phase ^= 1;
+        }
+        if (!ok && lane == 0) atomicCAS(err_flag, 0, kTcErrEpilogue);
+    }
+
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    tc::tc_fence_after_sync();
+    if (warp == 1) tc::tmem_dealloc(tmem_base, S::kTmemCols);
+}
+
+} // namespace sk

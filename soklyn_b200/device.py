@@ -67,6 +67,10 @@ class GpuContext:
         self.stream = stream
         self._check(self.lib.sk_ctx_set_stream(self.handle, C.c_void_p(stream.cuda_stream)))
 
+    def set_gemm_engine(self, ffma_only: bool):
+        """Force the FFMA GEMM (True) or let the library pick the tensor-core kernel where it can (False)."""
+        self._check(self.lib.sk_ctx_set_option(self.handle, 0, int(ffma_only)))
+
     def reserve(self, workspace_bytes: int):
         self._check(self.lib.sk_ctx_reserve(self.handle, workspace_bytes))
 

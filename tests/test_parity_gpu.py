@@ -100,3 +100,36 @@ def test_dropout_mask_bit_exact_full_size(gpu_ctx):
         keep = (s.astype(np.float32) / np.float32(4294967296.0)) >= np.float32(0.1)
         assert np.array_equal(m != 0, keep)
         assert abs(keep.mean() - 0.9) < 0.01
+
+
+TC_SPECS = [
+    SMALL4,
+    scaled(CONFIGS[4], dims=(72, 200, 136, 24), batch=100, name="tc_ragged_tiles"),          # no dimension fills a tile
+    scaled(CONFIGS[3], dims=(512, 384, 256, 64), batch=300, name="tc_layernorm_dropout"),
+    scaled(CONFIGS[2], dims=(784, 256, 64, 256, 784), batch=256, name="tc_autoencoder"),
+    scaled(CONFIGS[4], dims=(256, 1024, 256), batch=640, precision="bf16", name="tc_bf16"),
+]
+
+
+@pytest.mark.parametrize("spec", TC_SPECS, ids=lambda s: s.name)
+def test_tensor_core_gemm_matches_ffma_gemm(gpu_ctx, spec):
+    """The tcgen05 kernel and the FFMA kernel compute the same products from the same 16-bit
+    operands with f32 accumulation; only the summation order differs."""
+    w = configs.make_weights(spec)
+    x, t, _ = configs.make_data(spec)
+    try:
+        gpu_ctx.set_gemm_engine(True)
+        fnet, floss = H.run_device(gpu_ctx, spec, w, x, t, 2)
+        fstate = [H.device_state(gpu_ctx, l) for l in fnet.get_layers()]
+    finally:
+        gpu_ctx.set_gemm_engine(False)
+    tnet, tloss = H.run_device(gpu_ctx, spec, w, x, t, 2)
+    tstate = [H.device_state(gpu_ctx, l) for l in tnet.get_layers()]
+    np.testing.assert_allclose(tloss, floss, rtol=2e-3)
+    for i, (a, b) in enumerate(zip(tstate, fstate)):
+        for name in ("prenorm", "preact", "out", "grad", "d_prenorm", "dm_w", "dm_b", "d_norm_w"):
+            if name in a:
+                e = H.relerr(a[name], b[name])
+                tol = 4e-3 if spec.precision == "f16" else 1.6e-2   # a couple of ulps of the storage type
+                assert e <= tol, f"layer {i} {name}: tensor-core vs FFMA relative error {e:.3e}"
+        assert np.array_equal(a["mask"], b["mask"])
