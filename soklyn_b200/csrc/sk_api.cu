@@ -165,6 +165,8 @@ Optim make_optim(const sk_optim *o, uint32_t step) {
     r.kind = o->kind; r.beta1 = o->beta1; r.beta2 = o->beta2; r.epsilon = o->epsilon; r.nesterov = o->nesterov;
     r.bc1 = 1.0f - powf(o->beta1, (float)step);
     r.bc2 = 1.0f - powf(o->beta2, (float)step);
+    r.inv_bc1 = 1.0f / r.bc1;
+    r.inv_bc2 = 1.0f / r.bc2;
     return r;
 }
 
@@ -240,9 +242,12 @@ int forward_impl(sk_ctx *c, const sk_dense *L, const void *x, uint32_t batch, ui
     } else {
         const size_t cache_bytes = (size_t)L->N * sizeof(float);
         const bool cached = cache_bytes <= c->smem_optin;
-        norm_rows_kernel<T><<<batch, kRowThreads, cached ? cache_bytes : 0, c->stream>>>(
+        // rows stream straight from global memory (the second pass hits L2): no shared memory,
+        // so eight blocks fit an SM; the shared-memory row cache is kept for rows of odd length
+        const bool use_cache = cached && !vec;
+        norm_rows_kernel<T><<<batch, kRowThreads, use_cache ? cache_bytes : 0, c->stream>>>(
             (const T *)L->prenorm, (const T *)L->norm_w, (const T *)L->norm_b, (T *)L->centered, (T *)L->preact,
-            (T *)L->predrop, (T *)L->out, (T *)L->mask, (T *)L->norm_rstd, L->N, L->norm, ad, vec, cached);
+            (T *)L->predrop, (T *)L->out, (T *)L->mask, (T *)L->norm_rstd, L->N, L->norm, ad, vec, use_cache);
     }
     c->launches++;
     return check_cuda(c, cudaGetLastError(), "forward norm");
@@ -260,6 +265,18 @@ int output_error_impl(sk_ctx *c, const sk_dense *L, const void *target, uint32_t
     }
     const uint32_t warps = kRowThreads / 32;
     ProfScope ps(c, SK_PROF_OUTPUT_ERROR);
+    if (act != SK_ACT_SOFTMAX && layer_vec_ok(L) && aligned16(target)) {
+        const size_t total = (size_t)rows * (L->N / 8);
+        size_t blocks = (total + kRowThreads - 1) / kRowThreads;
+        const size_t cap = (size_t)c->num_sms * 16;
+        if (blocks > cap) blocks = cap;
+        output_error_elem_kernel<T><<<(uint32_t)blocks, kRowThreads, 0, c->stream>>>(
+            (const T *)L->out, (const T *)L->preact, (const T *)target, master_of<T>(L->master_norm_w, L->norm_w), L->grad,
+            L->d_prenorm, L->d_norm_w, L->d_norm_b, L->dtype == SK_F32 ? nullptr : (T *)L->d_prenorm_lp,
+            (const T *)L->norm_rstd, (const T *)L->centered, (const T *)L->prenorm, rows, L->N, loss, L->norm, act, leaky);
+        c->launches++;
+        return check_cuda(c, cudaGetLastError(), "output error");
+    }
     output_error_kernel<T><<<(rows + warps - 1) / warps, kRowThreads, 0, c->stream>>>(
         (T *)L->out, (const T *)L->preact, (const T *)target, master_of<T>(L->master_norm_w, L->norm_w), L->grad,
         L->d_prenorm, L->d_norm_w, L->d_norm_b, L->dtype == SK_F32 ? nullptr : (T *)L->d_prenorm_lp,

@@ -74,6 +74,102 @@ __device__ __forceinline__ float activation_derivative(uint32_t act, float delta
     }
 }
 
+// ---- the same on runs of V values, with the mode switch outside the element loop --------
+// FAST selects the hardware approximations (ex2/lg2/rcp.approx, ~2^-21 relative) in place of
+// the IEEE library routines. It is used only where results are stored in a 16-bit type,
+// whose own rounding (2^-11 / 2^-8) is far coarser.
+template <bool FAST> __device__ __forceinline__ float x_exp(float x) { return FAST ? __expf(x) : expf(x); }
+template <bool FAST> __device__ __forceinline__ float x_log(float x) { return FAST ? __logf(x) : logf(x); }
+template <bool FAST> __device__ __forceinline__ float x_div(float a, float b) { return FAST ? __fdividef(a, b) : a / b; }
+template <bool FAST> __device__ __forceinline__ float x_tanh(float x) {
+    if (!FAST) return tanhf(x);
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <bool FAST, int V>
+__device__ __forceinline__ void activation_v(uint32_t act, const float (&x)[V], float (&y)[V], float leaky) {
+    switch (act) {
+    case 1:
+#pragma unroll
+        for (int j = 0; j < V; ++j) y[j] = x_div<FAST>(1.0f, 1.0f + x_exp<FAST>(-x[j]));
+        break;
+    case 2:
+#pragma unroll
+        for (int j = 0; j < V; ++j) y[j] = fmaxf(0.0f, x[j]);
+        break;
+    case 3:
+#pragma unroll
+        for (int j = 0; j < V; ++j) y[j] = x[j] > 0.0f ? x[j] : leaky * x[j];
+        break;
+    case 4:
+#pragma unroll
+        for (int j = 0; j < V; ++j) y[j] = x_tanh<FAST>(x[j]);
+        break;
+    case 6:
+#pragma unroll
+        for (int j = 0; j < V; ++j) y[j] = x_div<FAST>(x[j], 1.0f + x_exp<FAST>(-x[j]));
+        break;
+    case 7:
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            const float ex = x_exp<FAST>(x[j]);
+            const float sp = x[j] > 20.0f ? x[j] : x_log<FAST>(1.0f + ex);
+            const float es = x_exp<FAST>(sp), esi = x_div<FAST>(1.0f, es);
+            y[j] = x[j] * x_div<FAST>(es - esi, es + esi);
+        }
+        break;
+    default:
+#pragma unroll
+        for (int j = 0; j < V; ++j) y[j] = x[j];
+        break;
+    }
+}
+
+// d[j] <- d[j] * act'(.) from the stored activation output and input
+template <bool FAST, int V>
+__device__ __forceinline__ void activation_derivative_v(uint32_t act, float (&d)[V], const float (&out_v)[V],
+                                                        const float (&in_x)[V], float leaky) {
+    switch (act) {
+    case 1:
+#pragma unroll
+        for (int j = 0; j < V; ++j) d[j] *= out_v[j] * (1.0f - out_v[j]);
+        break;
+    case 2:
+#pragma unroll
+        for (int j = 0; j < V; ++j) d[j] *= out_v[j] > 0.0f ? 1.0f : 0.0f;
+        break;
+    case 3:
+#pragma unroll
+        for (int j = 0; j < V; ++j) d[j] *= out_v[j] > 0.0f ? 1.0f : leaky;
+        break;
+    case 4:
+#pragma unroll
+        for (int j = 0; j < V; ++j) d[j] *= 1.0f - out_v[j] * out_v[j];
+        break;
+    case 6:
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            const float sg = x_div<FAST>(1.0f, 1.0f + x_exp<FAST>(-in_x[j]));
+            d[j] *= sg + out_v[j] * (1.0f - sg);
+        }
+        break;
+    case 7:
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            const float ex = x_exp<FAST>(in_x[j]);
+            const float sp = in_x[j] > 20.0f ? in_x[j] : x_log<FAST>(1.0f + ex);
+            const float es = x_exp<FAST>(sp), esi = x_div<FAST>(1.0f, es);
+            const float th = x_div<FAST>(es - esi, es + esi);
+            const float sg = x_div<FAST>(ex, 1.0f + ex);
+            d[j] *= th + in_x[j] * sg * (1.0f - th * th);
+        }
+        break;
+    default: break;
+    }
+}
+
 // ---- dropout hash: math.cuh:45-53; the result must match bit for bit -----------------------
 __device__ __forceinline__ float dropout_uniform(uint32_t col, uint32_t row, uint32_t seed) {
     uint32_t s = (row * 1103515245u) ^ (col * 0x4C957F2Du) ^ seed;
@@ -112,6 +208,7 @@ struct Optim {
     float beta1, beta2, epsilon;
     uint32_t nesterov;
     float bc1, bc2;      // 1 - beta^step, computed once on the host with powf
+    float inv_bc1, inv_bc2;
 };
 
 struct Hyper {
@@ -145,6 +242,35 @@ __device__ __forceinline__ float optimiser_step(float p, float &v, float &mo, fl
         p -= u;
     }
     return p;
+}
+
+__device__ __forceinline__ float sqrt_approx(float x) {
+    float y;
+    asm("sqrt.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// The same step with the two bias corrections as multiplications by host-side reciprocals and
+// the final quotient through rcp/sqrt approximations (relative error ~1e-7 on the update).
+__device__ __forceinline__ float optimiser_step_fast(float p, float &v, float &mo, float acc, const Optim &o,
+                                                     const Hyper &h, bool apply_regu) {
+    const float g = acc * h.inv_m;
+    if (apply_regu && h.regu) {
+        const float sign = p > 0.0f ? 1.0f : (p < 0.0f ? -1.0f : 0.0f);
+        if (h.regu == 1) p -= h.regu_coeff * sign;
+        if (h.regu == 2) p -= 2.0f * h.regu_coeff * p;
+    }
+    float u;
+    if (o.kind == 0) {
+        v = o.beta1 * v + g;
+        u = h.lr * (o.nesterov ? g + o.beta1 * v : v);
+    } else {
+        mo = o.beta1 * mo + (1.0f - o.beta1) * g;
+        v = o.beta2 * v + (1.0f - o.beta2) * g * g;
+        u = h.lr * __fdividef(mo * o.inv_bc1, sqrt_approx(v * o.inv_bc2) + o.epsilon);
+    }
+    u = fminf(fmaxf(u, -h.clamp), h.clamp);
+    return p - u;
 }
 
 // ---- warp / block reductions ------------------------------------------------------------

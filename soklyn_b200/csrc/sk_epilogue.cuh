@@ -3,6 +3,14 @@
 // reference does in the kernels that follow its GEMM (bias, activation, dropout;
 // activation derivative, mask and normalisation backward; loss-scale removal and the
 // optimiser step). The same functors serve the FFMA kernel and the tcgen05 kernel.
+//
+// Two call forms:
+//   run<V>(row, col0, acc, ncols)            everything at once (FFMA kernel, ragged edges)
+//   cols(col0) / prefetch(...) / finish(...) for the tensor-core kernel, whose epilogue threads
+//       keep one column group for several rows: cols() loads what depends on the columns only
+//       (bias, normalisation weights) once, prefetch() issues the raw loads of the next row's
+//       run before the current one is finished, finish() consumes them. These are used only
+//       when every tensor allows 128-bit accesses (vec_ok) and the run has all 8 columns.
 #pragma once
 
 #include "sk_device.cuh"
@@ -37,6 +45,18 @@ __device__ __forceinline__ void store_run(T *p, bool vec, const float (&in)[V]) 
         for (int i = 0; i < V; ++i) p[i] = from_f32<T>(in[i]);
     }
 }
+
+// Raw (unconverted) run of V elements, for loads issued ahead of their use.
+template <typename T, int V> __device__ __forceinline__ Pack<T, V> load_pack(const T *p) {
+    return *reinterpret_cast<const Pack<T, V> *>(p);
+}
+template <typename T, int V> __device__ __forceinline__ void unpack(const Pack<T, V> &pk, float (&out)[V]) {
+#pragma unroll
+    for (int i = 0; i < V; ++i) out[i] = to_f32(pk.v[i]);
+}
+
+struct NoPre {};
+template <typename T> constexpr bool kFastMath = sizeof(T) == 2;   // 16-bit storage hides approximate math
 
 // ---- forward: Z = X.W + b, then (no normalisation) activation and dropout ------------------
 // Reference: ffn/forward.cu:8-28 (bias), :130-161 (activation + dropout).
@@ -73,27 +93,16 @@ template <typename T> struct EpiForward {
         }
     }
 
+    // vector path; b = bias of these columns (zeros when unused)
     template <int V>
-    __device__ __forceinline__ void run(uint32_t row, uint32_t col0, const float (&acc)[V], uint32_t ncols) const {
-        if (!(vec_ok && ncols == V)) {
-            for (uint32_t j = 0; j < ncols; ++j) one(row, col0 + j, acc[j]);
-            return;
-        }
+    __device__ __forceinline__ void core(uint32_t row, uint32_t col0, const float (&acc)[V], const float (&b)[V]) const {
         const size_t idx = (size_t)row * N + col0;
         float zv[V], a[V], o[V], mk[V];
-        if (bias) {
-            float b[V];
-            load_run<T, V>(bias + col0, true, b);
 #pragma unroll
-            for (int j = 0; j < V; ++j) zv[j] = round_to<T>(acc[j] + b[j]);
-        } else {
-#pragma unroll
-            for (int j = 0; j < V; ++j) zv[j] = round_to<T>(acc[j]);
-        }
+        for (int j = 0; j < V; ++j) zv[j] = round_to<T>(acc[j] + b[j]);
         store_run<T, V>(z + idx, true, zv);
         if (has_norm) return;
-#pragma unroll
-        for (int j = 0; j < V; ++j) a[j] = activation(act, zv[j], leaky);
+        activation_v<kFastMath<T>, V>(act, zv, a, leaky);
         store_run<T, V>(predrop + idx, true, a);
         if (use_dropout) {
             const uint32_t grow = row + row_offset;
@@ -109,6 +118,35 @@ template <typename T> struct EpiForward {
         } else {
             store_run<T, V>(out + idx, true, a);
         }
+    }
+
+    template <int V>
+    __device__ __forceinline__ void run(uint32_t row, uint32_t col0, const float (&acc)[V], uint32_t ncols) const {
+        if (!(vec_ok && ncols == V)) {
+            for (uint32_t j = 0; j < ncols; ++j) one(row, col0 + j, acc[j]);
+            return;
+        }
+        float b[V];
+        if (bias) load_run<T, V>(bias + col0, true, b);
+        else {
+#pragma unroll
+            for (int j = 0; j < V; ++j) b[j] = 0.0f;
+        }
+        core<V>(row, col0, acc, b);
+    }
+
+    struct Cols { float b[8]; };
+    using Pre = NoPre;
+    __device__ __forceinline__ void cols(uint32_t col0, Cols &c) const {
+        if (bias) load_run<T, 8>(bias + col0, true, c.b);
+        else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) c.b[j] = 0.0f;
+        }
+    }
+    __device__ __forceinline__ void prefetch(uint32_t, uint32_t, Pre &) const {}
+    __device__ __forceinline__ void finish(uint32_t row, uint32_t col0, const float (&acc)[8], const Pre &, const Cols &c) const {
+        core<8>(row, col0, acc, c.b);
     }
 };
 
@@ -138,6 +176,47 @@ template <typename T> struct EpiHidden {
         if (d_prenorm_lp) d_prenorm_lp[idx] = from_f32<T>(g.d_prenorm);
     }
 
+    // vector path on unpacked inputs of one run. nw: normalisation weights of the columns,
+    // rs: rstd per column (BatchNorm) or the row's rstd in every slot (RMSNorm / LayerNorm).
+    template <int V>
+    __device__ __forceinline__ void core(uint32_t row, uint32_t col0, const float (&acc)[V], const float (&pd)[V],
+                                         const float (&pa)[V], const float (&mk)[V], const float (&xv)[V],
+                                         const float (&nw)[V], const float (&rs)[V]) const {
+        const size_t idx = (size_t)row * N + col0;
+        float gr[V], dp[V], gw[V], gb[V];
+#pragma unroll
+        for (int j = 0; j < V; ++j) gr[j] = acc[j];
+        activation_derivative_v<kFastMath<T>, V>(act, gr, pd, pa, leaky);
+#pragma unroll
+        for (int j = 0; j < V; ++j) gr[j] *= mk[j];
+        if (norm == 0) {
+#pragma unroll
+            for (int j = 0; j < V; ++j) { dp[j] = gr[j]; gw[j] = 0.0f; gb[j] = 0.0f; }
+        } else if (norm == 1) {
+#pragma unroll
+            for (int j = 0; j < V; ++j) {
+                const float r = rs[j];
+                gw[j] = gr[j] * xv[j] * r;
+                gb[j] = 0.0f;
+                dp[j] = nw[j] * r * (gr[j] - r * r * xv[j] * xv[j] * inv_n);
+            }
+        } else {
+            const float inv = norm == 2 ? inv_n : inv_m;
+#pragma unroll
+            for (int j = 0; j < V; ++j) {
+                const float r = rs[j];
+                gb[j] = gr[j];
+                gw[j] = gr[j] * xv[j] * r;
+                dp[j] = nw[j] * r * (gr[j] - gr[j] * inv - r * r * xv[j] * xv[j] * gr[j] * inv);
+            }
+        }
+        store_run<float, V>(grad + idx, true, gr);
+        store_run<float, V>(d_prenorm + idx, true, dp);
+        store_run<float, V>(d_norm_w + idx, true, gw);
+        store_run<float, V>(d_norm_b + idx, true, gb);
+        if (d_prenorm_lp) store_run<T, V>(d_prenorm_lp + idx, true, dp);
+    }
+
     template <int V>
     __device__ __forceinline__ void run(uint32_t row, uint32_t col0, const float (&acc)[V], uint32_t ncols) const {
         if (!(vec_ok && ncols == V)) {
@@ -146,7 +225,6 @@ template <typename T> struct EpiHidden {
         }
         const size_t idx = (size_t)row * N + col0;
         float pd[V], pa[V], mk[V], xv[V], nw[V], rs[V];
-        float gr[V], dp[V], gw[V], gb[V];
         load_run<T, V>(predrop + idx, true, pd);
         load_run<T, V>(preact + idx, true, pa);
         load_run<T, V>(mask + idx, true, mk);
@@ -154,23 +232,44 @@ template <typename T> struct EpiHidden {
         else if (norm >= 2) load_run<T, V>(centered + idx, true, xv);
         if (norm) load_run<float, V>(norm_w + col0, true, nw);
         if (norm == 3) load_run<T, V>(rstd + col0, true, rs);
-        const float rrow = (norm == 1 || norm == 2) ? to_f32(rstd[row]) : 0.0f;
+        else if (norm) {
+            const float r = to_f32(rstd[row]);
 #pragma unroll
-        for (int j = 0; j < V; ++j) {
-            const float delta = mk[j] * activation_derivative(act, acc[j], pd[j], pa[j], leaky);
-            gr[j] = delta;
-            const float r = norm == 3 ? rs[j] : rrow;
-            const NormGrad g = norm_gradients(norm, delta, norm ? xv[j] : 0.0f, norm ? xv[j] : 0.0f, r,
-                                              norm ? nw[j] : 0.0f, inv_n, inv_m);
-            dp[j] = g.d_prenorm;
-            gw[j] = g.d_norm_w;
-            gb[j] = g.d_norm_b;
+            for (int j = 0; j < V; ++j) rs[j] = r;
         }
-        store_run<float, V>(grad + idx, true, gr);
-        store_run<float, V>(d_prenorm + idx, true, dp);
-        store_run<float, V>(d_norm_w + idx, true, gw);
-        store_run<float, V>(d_norm_b + idx, true, gb);
-        if (d_prenorm_lp) store_run<T, V>(d_prenorm_lp + idx, true, dp);
+        core<V>(row, col0, acc, pd, pa, mk, xv, nw, rs);
+    }
+
+    struct Cols { float nw[8], rs[8]; };
+    struct Pre { Pack<T, 8> pd, pa, mk, xv; T rrow; };
+    __device__ __forceinline__ void cols(uint32_t col0, Cols &c) const {
+        if (norm) load_run<float, 8>(norm_w + col0, true, c.nw);
+        if (norm == 3) load_run<T, 8>(rstd + col0, true, c.rs);
+    }
+    __device__ __forceinline__ void prefetch(uint32_t row, uint32_t col0, Pre &p) const {
+        const size_t idx = (size_t)row * N + col0;
+        p.pd = load_pack<T, 8>(predrop + idx);
+        p.pa = load_pack<T, 8>(preact + idx);
+        p.mk = load_pack<T, 8>(mask + idx);
+        if (norm == 1) p.xv = load_pack<T, 8>(prenorm + idx);
+        else if (norm >= 2) p.xv = load_pack<T, 8>(centered + idx);
+        if (norm == 1 || norm == 2) p.rrow = rstd[row];
+    }
+    __device__ __forceinline__ void finish(uint32_t row, uint32_t col0, const float (&acc)[8], const Pre &p, const Cols &c) const {
+        float pd[8], pa[8], mk[8], xv[8], rs[8];
+        unpack<T, 8>(p.pd, pd);
+        unpack<T, 8>(p.pa, pa);
+        unpack<T, 8>(p.mk, mk);
+        if (norm) unpack<T, 8>(p.xv, xv);
+        if (norm == 3) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) rs[j] = c.rs[j];
+        } else if (norm) {
+            const float r = to_f32(p.rrow);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) rs[j] = r;
+        }
+        core<8>(row, col0, acc, pd, pa, mk, xv, c.nw, rs);
     }
 };
 
@@ -217,6 +316,29 @@ template <typename T> struct EpiWeightUpdate {
             }
         }
     }
+
+    struct Cols {};
+    struct Pre { Pack<float, 8> p, v, m; };
+    __device__ __forceinline__ void cols(uint32_t, Cols &) const {}
+    __device__ __forceinline__ void prefetch(uint32_t row, uint32_t col0, Pre &q) const {
+        const size_t idx = (size_t)row * N + col0;
+        q.p = load_pack<float, 8>(master + idx);
+        q.v = load_pack<float, 8>(dv + idx);
+        q.m = load_pack<float, 8>(dm + idx);
+    }
+    __device__ __forceinline__ void finish(uint32_t row, uint32_t col0, const float (&acc)[8], const Pre &q, const Cols &) const {
+        const size_t idx = (size_t)row * N + col0;
+        float p[8], v[8], m[8];
+        unpack<float, 8>(q.p, p);
+        unpack<float, 8>(q.v, v);
+        unpack<float, 8>(q.m, m);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) p[j] = optimiser_step_fast(p[j], v[j], m[j], acc[j] * kLossScaleInv, opt, hyp, true);
+        store_run<float, 8>(dv + idx, true, v);
+        store_run<float, 8>(dm + idx, true, m);
+        store_run<float, 8>(master + idx, true, p);
+        if ((void *)w != (void *)master) store_run<T, 8>(w + idx, true, p);
+    }
 };
 
 // ---- plain f32 store (raw batch sums for the data-parallel exchange) ------------------------------
@@ -229,6 +351,14 @@ struct EpiStoreF32 {
         const size_t idx = (size_t)row * N + col0;
         if (vec_ok && ncols == V) store_run<float, V>(c + idx, true, acc);
         else for (uint32_t j = 0; j < ncols; ++j) c[idx + j] = acc[j];
+    }
+
+    struct Cols {};
+    using Pre = NoPre;
+    __device__ __forceinline__ void cols(uint32_t, Cols &) const {}
+    __device__ __forceinline__ void prefetch(uint32_t, uint32_t, Pre &) const {}
+    __device__ __forceinline__ void finish(uint32_t row, uint32_t col0, const float (&acc)[8], const Pre &, const Cols &) const {
+        store_run<float, 8>(c + (size_t)row * N + col0, true, acc);
     }
 };
 

@@ -152,19 +152,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll 1
             for (uint32_t c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32) {
                 if (n0 + c0 >= N) break;              // uniform per warp
+                // runs of this chunk: pass p covers rows 8p + lane/4, columns 8*(lane%4) .. +8
+                const uint32_t cc = (lane & 3) * 8, col = n0 + c0 + cc;
+                const uint32_t row_base = m0 + quarter * 32 + (lane >> 2);
+                const bool col_ok = col < N;
+                const uint32_t ncols = col_ok ? min(8u, N - col) : 0u;
+                // The fast path needs 128-bit accesses and a full run of 8 columns; everything
+                // else (ragged right edge, unaligned tensors) goes through run<8>.
+                const bool fast = epi.vec_ok && ncols == 8;
+                // One run ahead: the loads of pass p+1 are in flight while pass p is finished. The
+                // pass loop is deliberately not unrolled: the epilogue body (every activation and
+                // normalisation case) must exist once, or the kernel outgrows the instruction cache.
+                typename Epi::Cols cols;
+                typename Epi::Pre cur, nxt;
+                if (fast) {
+                    epi.cols(col, cols);
+                    if (row_base < M) epi.prefetch(row_base, col, cur);
+                }
                 float v[32];
                 tc::tmem_ld_32x32(tmem_base + ((quarter * 32) << 16) + acc * BN + c0, v);
 #pragma unroll
                 for (int j = 0; j < 32; ++j) buf[lane * 33 + j] = v[j];
                 __syncwarp();
-#pragma unroll
-                for (int pass = 0; pass < 4; ++pass) {
-                    const uint32_t rr = pass * 8 + (lane >> 2), cc = (lane & 3) * 8;
+#pragma unroll 1
+                for (int p = 0; p < 4; ++p) {
+                    const uint32_t rr = p * 8 + (lane >> 2), row = m0 + quarter * 32 + rr;
+                    if (fast && p < 3 && row + 8 < M) epi.prefetch(row + 8, col, nxt);
                     float r[8];
 #pragma unroll
                     for (int j = 0; j < 8; ++j) r[j] = buf[rr * 33 + cc + j];
-                    const uint32_t row = m0 + quarter * 32 + rr, col = n0 + c0 + cc;
-                    if (row < M && col < N) epi.template run<8>(row, col, r, min(8u, N - col));
+                    if (col_ok && row < M) {
+                        if (fast) epi.finish(row, col, r, cur, cols);
+                        else epi.template run<8>(row, col, r, ncols);
+                    }
+                    cur = nxt;
                 }
                 __syncwarp();
             }

@@ -23,9 +23,9 @@ __device__ __forceinline__ void act_drop_store(const ActDrop &ad, const float (&
     float a[V], o[V], mk[V];
     const uint32_t grow = row + ad.row_offset;
     const float scale = 1.0f / (1.0f - ad.mask_coeff);
+    activation_v<kFastMath<T>, V>(ad.act, pre, a, ad.leaky);
 #pragma unroll
     for (int j = 0; j < V; ++j) {
-        a[j] = activation(ad.act, pre[j], ad.leaky);
         const bool keep = ad.use_dropout ? dropout_keep(col0 + j, grow, ad.seed, ad.mask_coeff) : true;
         mk[j] = keep ? scale : 0.0f;
         o[j] = ad.use_dropout ? (keep ? a[j] * scale : 0.0f) : a[j];
@@ -44,8 +44,9 @@ __device__ __forceinline__ void act_drop_store(const ActDrop &ad, const float (&
 }
 
 // RMSNorm (norm 1) / LayerNorm (norm 2) of one row per block, fused with activation and
-// dropout: reads prenorm once from HBM (the row is kept in shared memory as f32 when
-// `cached`), writes centered, preact, predrop, out, (mask) and rstd[row].
+// dropout: reads prenorm once from HBM (later passes over the row hit L2, or shared memory
+// when `cached`), writes centered, preact, predrop, out, (mask) and rstd[row]. The output loop
+// is kept rolled so that the activation code exists once (instruction-cache footprint).
 // Reference: ffn/forward.cu:44-73 (RMS, products in T arithmetic), :74-126 (LayerNorm).
 template <typename T>
 __global__ void __launch_bounds__(kRowThreads)
@@ -127,6 +128,7 @@ norm_rows_kernel(const T *__restrict__ prenorm, const T *__restrict__ norm_w, co
         act_drop_store<T, V>(ad, pre, row, col0, idx, predrop, out, mask, vec, ncols);
     };
     if (vec_ok) {
+#pragma unroll 1
         for (uint32_t c = threadIdx.x; c < nvec; c += blockDim.x) {
             float x[V];
             if (cached) {
@@ -238,6 +240,52 @@ output_error_kernel(T *__restrict__ out, const T *__restrict__ preact, const T *
         d_norm_w[idx] = g.d_norm_w;
         d_norm_b[idx] = g.d_norm_b;
         if (d_prenorm_lp) d_prenorm_lp[idx] = from_f32<T>(dp);
+    }
+}
+
+// Output-layer delta without softmax: purely element-wise, 8 elements per thread with 128-bit
+// accesses (ffn/backward.cu:12-56). Requires N % 8 == 0 and 16-byte aligned tensors.
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+output_error_elem_kernel(const T *__restrict__ out, const T *__restrict__ preact, const T *__restrict__ target,
+                         const float *__restrict__ norm_w, float *__restrict__ grad, float *__restrict__ d_prenorm,
+                         float *__restrict__ d_norm_w, float *__restrict__ d_norm_b, T *__restrict__ d_prenorm_lp,
+                         const T *__restrict__ rstd, const T *__restrict__ centered, const T *__restrict__ prenorm,
+                         uint32_t M, uint32_t N, uint32_t err_mode, uint32_t norm, uint32_t act, float leaky) {
+    constexpr int V = 8;
+    const uint32_t nvec = N / V;
+    const size_t total = (size_t)M * nvec, stride = (size_t)gridDim.x * blockDim.x;
+    const float inv_m = 1.0f / (float)M, inv_n = 1.0f / (float)N;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const uint32_t row = (uint32_t)(i / nvec), col0 = (uint32_t)(i % nvec) * V;
+        const size_t idx = (size_t)row * N + col0;
+        float o[V], pa[V], tg[V], xv[V], nw[V], rs[V], gr[V], dp[V], gw[V], gb[V];
+        load_run<T, V>(out + idx, true, o);
+        load_run<T, V>(target + idx, true, tg);
+        if (err_mode == 0) load_run<T, V>(preact + idx, true, pa);
+        if (norm == 1) load_run<T, V>(prenorm + idx, true, xv);
+        else if (norm >= 2) load_run<T, V>(centered + idx, true, xv);
+        if (norm) load_run<float, V>(norm_w + col0, true, nw);
+        if (norm == 3) load_run<T, V>(rstd + col0, true, rs);
+        const float rrow = (norm == 1 || norm == 2) ? to_f32(rstd[row]) : 0.0f;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            const float a = activation(act, o[j], leaky);
+            float delta = 0.0f;
+            if (err_mode == 0) delta = activation_derivative(act, a - tg[j], a, pa[j], leaky);
+            else if (err_mode == 2 && act == 1) delta = a - tg[j];
+            gr[j] = delta;
+            const NormGrad g = norm_gradients(norm, delta, norm ? xv[j] : 0.0f, norm ? xv[j] : 0.0f,
+                                              norm == 3 ? rs[j] : rrow, norm ? nw[j] : 0.0f, inv_n, inv_m);
+            dp[j] = g.d_prenorm * kLossScale;
+            gw[j] = g.d_norm_w;
+            gb[j] = g.d_norm_b;
+        }
+        store_run<float, V>(grad + idx, true, gr);
+        store_run<float, V>(d_prenorm + idx, true, dp);
+        store_run<float, V>(d_norm_w + idx, true, gw);
+        store_run<float, V>(d_norm_b + idx, true, gb);
+        if (d_prenorm_lp) store_run<T, V>(d_prenorm_lp + idx, true, dp);
     }
 }
 

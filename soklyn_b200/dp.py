@@ -41,10 +41,10 @@ class DataParallelFFN:
             if layer.get_normalisation() == Normalisation.BatchNorm and world > 1:
                 raise log.InvalidConfiguration("BatchNorm is not supported under data parallelism")
         dev = context.device
+        layers = network.get_layers() if world > 1 else []
         self.dw = [torch.empty(l.get_weights().rows(), l.get_weights().cols(), device=dev, dtype=torch.float32)
-                   for l in network.get_layers()]
-        self.colsums = [torch.empty(3, l.get_weights().cols(), device=dev, dtype=torch.float32)
-                        for l in network.get_layers()]
+                   for l in layers]
+        self.colsums = [torch.empty(3, l.get_weights().cols(), device=dev, dtype=torch.float32) for l in layers]
         self.collectives = 0
 
     def forward(self, input: Tensor, use_dropout: bool, step: int):
@@ -71,6 +71,10 @@ class DataParallelFFN:
             x = outputs[i - 1] if i > 0 else input
             if i < last:
                 self.ctx.gpu_hidden_layer_error(layer, layers[i + 1], self.local_batch, self.global_batch)
+            if self.world == 1:   # nothing to exchange: dW GEMM with the optimiser step in its epilogue
+                tc1 = train_ctx.get_train_context(i)
+                self.ctx.gpu_backward_pass(layer, x, tc1, step)
+                continue
             self.ctx.gpu_backward_grads(layer, x, self.local_batch, self.dw[i], self.colsums[i])
             self._exchange(i)
             self.ctx.gpu_apply_update(layer, self.dw[i], self.colsums[i], self.global_batch,

@@ -1,0 +1,123 @@
+"""Host logic of data-parallel training on two CPU ranks (gloo): row sharding, the order of
+gradient exchange / update / hidden delta, and that both ranks apply the same summed gradient.
+The device calls are replaced by a recording fake; the kernels themselves are covered on a GPU."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+class _T:
+    def __init__(self, r, c):
+        self._r, self._c = r, c
+
+    def rows(self):
+        return self._r
+
+    def cols(self):
+        return self._c
+
+
+class _Layer:
+    def __init__(self, k, n, idx, log):
+        from soklyn_b200.function import Normalisation
+        self.k, self.n, self.idx, self.log = k, n, idx, log
+        self.norm = Normalisation.Disabled
+
+    def get_weights(self):
+        return _T(self.k, self.n)
+
+    def get_normalisation(self):
+        return self.norm
+
+    def forward(self, ctx, x, batch, use_dropout, step, row_offset=0):
+        self.log.append(("forward", self.idx, batch, row_offset))
+        return _T(batch, self.n)
+
+    def compute_loss(self, ctx, target, loss_config):
+        self.log.append(("loss", self.idx))
+
+
+class _Ctx:
+    """Stands in for GpuContext: rank r contributes (r+1)*(layer+1) to every gradient element."""
+
+    def __init__(self, rank, log):
+        self.device, self.rank, self.log = torch.device("cpu"), rank, log
+        self.applied = {}
+
+    def gpu_hidden_layer_error(self, cur, nxt, batch, batch_stat):
+        self.log.append(("hidden", cur.idx, nxt.idx, batch, batch_stat))
+
+    def gpu_backward_grads(self, layer, x, batch, dw, colsums):
+        self.log.append(("grads", layer.idx, batch))
+        dw.fill_((self.rank + 1) * (layer.idx + 1))
+        colsums.fill_(10.0 * (self.rank + 1))
+
+    def gpu_apply_update(self, layer, dw, colsums, batch_stat, train_ctx, step):
+        self.log.append(("apply", layer.idx, batch_stat))
+        self.applied[layer.idx] = (float(dw[0, 0]), float(dw.min()), float(dw.max()), float(colsums[2, -1]))
+
+    def gpu_backward_pass(self, layer, x, train_ctx, step):
+        self.log.append(("fused", layer.idx))
+
+
+def _worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from soklyn_b200.context import LossConfig, MultiLayerTrainContext
+    from soklyn_b200.dp import DataParallelFFN
+    from soklyn_b200.ffn import FeedForwardNetwork
+    from soklyn_b200.function import Activation, LossFunc, Optimiser
+    log = []
+    layers = [_Layer(6, 5, 0, log), _Layer(5, 4, 1, log), _Layer(4, 3, 2, log)]
+    ctx = _Ctx(rank, log)
+    dp = DataParallelFFN(ctx, FeedForwardNetwork(layers, 6), global_batch=8, rank=rank, world=world)
+    outs = dp.forward(_T(4, 6), False, 1)
+    opt = [Optimiser.Adam()] * 3
+    dp.backward(outs, _T(4, 3), _T(4, 6), LossConfig(LossFunc.MeanSquareLoss, Activation.Identity),
+                MultiLayerTrainContext(opt, opt, 8, 1e-3), 1)
+    q.put((rank, log, ctx.applied, dp.row_offset, dp.local_batch, dp.collectives))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_gradient_exchange_and_ordering():
+    world, port = 2, 29000 + os.getpid() % 2000
+    ctxm = mp.get_context("spawn")
+    q = ctxm.Queue()
+    procs = [ctxm.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted(q.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, log, applied, row_offset, local, collectives in results:
+        assert (row_offset, local) == (4 * rank, 4)
+        assert collectives == 6                                # dW + column sums per layer
+        assert [e for e in log if e[0] == "forward"] == [("forward", i, 4, 4 * rank) for i in range(3)]
+        for i in range(3):                                      # sum over ranks: (1 + 2) * (layer + 1)
+            first, lo, hi, cs = applied[i]
+            assert first == lo == hi == 3.0 * (i + 1) and cs == 30.0
+        order = [e[:2] for e in log if e[0] in ("loss", "hidden", "grads", "apply")]
+        assert order == [("loss", 2), ("grads", 2), ("apply", 2), ("hidden", 1), ("grads", 1), ("apply", 1),
+                         ("hidden", 0), ("grads", 0), ("apply", 0)]
+        assert all(e[3:] == (4, 8) for e in log if e[0] == "hidden")      # local rows, global 1/M
+        assert all(e[2] == 8 for e in log if e[0] == "apply")
+    assert results[0][2] == results[1][2]                       # both ranks step with identical gradients
+
+
+def test_shard_rows_and_single_rank_path():
+    sys.path.insert(0, ROOT)
+    from soklyn_b200 import log as sklog
+    from soklyn_b200.dp import shard_rows
+    assert shard_rows(8192, 3, 8) == (3072, 1024)
+    assert shard_rows(10, 0, 1) == (0, 10)
+    with pytest.raises(sklog.InvalidBatchSize):
+        shard_rows(10, 0, 4)
