@@ -162,6 +162,19 @@ int sk_apply_update(sk_ctx *ctx, const sk_dense *layer, const float *dw, const f
                     uint32_t batch_stat, const sk_optim *linear, const sk_optim *norm_opt,
                     float learn_rate, float grad_clamp, uint32_t step);
 
+/* Sharded form of the same exchange (no counterpart): sk_backward_grads_lp writes dW in the block's
+ * storage type, already divided by batch_stat (loss scale x512 kept), so that ranks can
+ * reduce-scatter half the bytes; sk_apply_update_rows steps rows [row0, row0 + nrows) of the weight
+ * matrix (master, moments and the 16-bit copy) from the summed gradient of just those rows;
+ * sk_apply_vector_update steps bias and normalisation parameters from summed column sums. */
+int sk_backward_grads_lp(sk_ctx *ctx, const sk_dense *layer, const void *x, uint32_t x_rows, uint32_t batch,
+                         uint32_t batch_stat, void *grad, float *colsums);
+int sk_apply_update_rows(sk_ctx *ctx, const sk_dense *layer, const void *grad, uint32_t row0, uint32_t nrows,
+                         const sk_optim *linear, float learn_rate, float grad_clamp, uint32_t step);
+int sk_apply_vector_update(sk_ctx *ctx, const sk_dense *layer, const float *colsums, uint32_t batch_stat,
+                           const sk_optim *linear, const sk_optim *norm_opt, float learn_rate, float grad_clamp,
+                           uint32_t step);
+
 /* No counterpart in the reference. Column sums over the batch of d_prenorm, d_norm_w and
  * d_norm_b, written to colsums f32 [3 x N] exactly as sk_backward_grads writes them, but
  * without a context and without allocating: for callers that are not allowed to allocate

@@ -112,6 +112,12 @@ _SIGS = {
                                     C.c_void_p, C.c_void_p]),
     "sk_apply_update": (C.c_int, [C.c_void_p, C.POINTER(SkDense), C.c_void_p, C.c_void_p, C.c_uint32,
                                   C.POINTER(SkOptim), C.POINTER(SkOptim), C.c_float, C.c_float, C.c_uint32]),
+    "sk_backward_grads_lp": (C.c_int, [C.c_void_p, C.POINTER(SkDense), C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32,
+                                       C.c_void_p, C.c_void_p]),
+    "sk_apply_update_rows": (C.c_int, [C.c_void_p, C.POINTER(SkDense), C.c_void_p, C.c_uint32, C.c_uint32,
+                                       C.POINTER(SkOptim), C.c_float, C.c_float, C.c_uint32]),
+    "sk_apply_vector_update": (C.c_int, [C.c_void_p, C.POINTER(SkDense), C.c_void_p, C.c_uint32, C.POINTER(SkOptim),
+                                         C.POINTER(SkOptim), C.c_float, C.c_float, C.c_uint32]),
     "sk_column_sums_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32,
                                         C.c_uint32, C.c_uint32]),
     "sk_cast": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_size_t]),

@@ -393,6 +393,61 @@ int backward_grads_impl(sk_ctx *c, const sk_dense *L, const void *x, uint32_t ba
     return rc;
 }
 
+// dW as the storage type, already divided by batch_stat (the loss scale stays in), plus the raw
+// f32 column sums: the payload of the sharded data-parallel exchange.
+template <typename T>
+int backward_grads_lp_impl(sk_ctx *c, const sk_dense *L, const void *x, uint32_t batch, uint32_t batch_stat, void *g,
+                           float *colsums) {
+    int rc = SK_OK;
+    const uint32_t nblocks = launch_colsum_partial(c, L, batch, &rc);
+    if (rc) return rc;
+    colsum_final_kernel<<<(3 * L->N + 255) / 256, 256, 0, c->stream>>>((const float *)c->workspace, colsums, L->N, nblocks);
+    c->launches++;
+    if ((rc = check_cuda(c, cudaGetLastError(), "column sums (final)"))) return rc;
+    EpiStoreScaled<T> epi{(T *)g, L->N, 1.0f / (float)batch_stat, L->N % 8 == 0 && aligned16(g)};
+    ProfScope ps(c, SK_PROF_GEMM_DW);
+    if (L->dtype == SK_F32)
+        rc = check_cuda(c, run_gemm<T, float, false, true>(c, L->dtype, (const T *)x, L->K, L->d_prenorm,
+                                                                    L->N, L->K, L->N, batch, epi), "weight gradient gemm");
+    else
+        rc = check_cuda(c, run_gemm<T, T, false, true>(c, L->dtype, (const T *)x, L->K,
+                                                                (const T *)L->d_prenorm_lp, L->N, L->K, L->N, batch, epi),
+                        "weight gradient gemm");
+    c->launches++;
+    return rc;
+}
+
+// Optimiser step on rows [row0, row0 + nrows) of the weight matrix from an averaged gradient of
+// the storage type, laid out as those rows only.
+template <typename T>
+int apply_update_rows_impl(sk_ctx *c, const sk_dense *L, const void *g, uint32_t row0, uint32_t nrows,
+                           const sk_optim *lin_, float lr, float clamp, uint32_t step) {
+    const Optim lin = make_optim(lin_, step);
+    const Hyper hyp{lr, clamp, 1.0f, L->regu, L->regu_coeff};   // the gradient is already averaged
+    const size_t off = (size_t)row0 * L->N, len = (size_t)nrows * L->N;
+    float *master = master_of<T>(L->master_w, L->w) + off;
+    T *w = (T *)L->w + off;
+    float *dv = L->dv_w + off, *dm = L->dm_w + off;
+    const bool vec = len % 8 == 0 && aligned16(g) && aligned16(w) && aligned16(master) && aligned16(dv) && aligned16(dm);
+    size_t blocks = (len / 8 + kRowThreads - 1) / kRowThreads;
+    const size_t cap = (size_t)c->num_sms * 8;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    ProfScope ps(c, SK_PROF_UPDATE);
+    weight_update_range_kernel<T, T><<<(uint32_t)blocks, kRowThreads, 0, c->stream>>>(
+        (const T *)g, kLossScaleInv, w, master, dv, dm, len, lin, hyp, vec);
+    c->launches++;
+    return check_cuda(c, cudaGetLastError(), "weight step (rows)");
+}
+
+template <typename T>
+int apply_vector_update_impl(sk_ctx *c, const sk_dense *L, const float *colsums, uint32_t batch_stat,
+                             const sk_optim *lin_, const sk_optim *nrm_, float lr, float clamp, uint32_t step) {
+    const Optim lin = make_optim(lin_, step), nrm = make_optim(nrm_, step);
+    const Hyper hyp{lr, clamp, 1.0f / (float)batch_stat, L->regu, L->regu_coeff};
+    return vector_update_launch<T>(c, L, colsums, 1, lin, nrm, hyp);
+}
+
 template <typename T>
 int apply_update_impl(sk_ctx *c, const sk_dense *L, const float *dw, const float *colsums, uint32_t batch_stat,
                       const sk_optim *lin_, const sk_optim *nrm_, float lr, float clamp, uint32_t step) {
@@ -640,6 +695,37 @@ int sk_apply_update(sk_ctx *c, const sk_dense *L, const float *dw, const float *
     if (batch_stat == 0) return fail(c, SK_ERR_INVALID_BATCH_SIZE, "Batch size must be more than zero.");
     if (lin->kind > 1 || nrm->kind > 1) return fail(c, SK_ERR_INVALID_CONFIGURATION, "optimiser ordinal out of range");
     return SK_DISPATCH(L->dtype, apply_update_impl, c, L, dw, colsums, batch_stat, lin, nrm, lr, clamp, step);
+}
+
+int sk_backward_grads_lp(sk_ctx *c, const sk_dense *L, const void *x, uint32_t x_rows, uint32_t batch,
+                         uint32_t batch_stat, void *grad, float *colsums) {
+    int rc = check_layer(c, L, true);
+    if (rc) return rc;
+    if (!x || !grad || !colsums) return fail(c, SK_ERR_NULL_POINTER, "input or output pointer is NULL");
+    if ((rc = check_batch(c, L, x_rows, batch))) return rc;
+    if (batch_stat == 0) return fail(c, SK_ERR_INVALID_BATCH_SIZE, "Batch size must be more than zero.");
+    return SK_DISPATCH(L->dtype, backward_grads_lp_impl, c, L, x, batch, batch_stat, grad, colsums);
+}
+
+int sk_apply_update_rows(sk_ctx *c, const sk_dense *L, const void *grad, uint32_t row0, uint32_t nrows,
+                         const sk_optim *lin, float lr, float clamp, uint32_t step) {
+    int rc = check_layer(c, L, true);
+    if (rc) return rc;
+    if (!grad || !lin) return fail(c, SK_ERR_NULL_POINTER, "gradient or optimiser pointer is NULL");
+    if (nrows == 0 || (uint64_t)row0 + nrows > L->K)
+        return fail(c, SK_ERR_MISMATCHED_DIMENSIONS, "rows [%u, %u) outside the %u rows of the weight matrix", row0, row0 + nrows, L->K);
+    if (lin->kind > 1) return fail(c, SK_ERR_INVALID_CONFIGURATION, "optimiser ordinal out of range");
+    return SK_DISPATCH(L->dtype, apply_update_rows_impl, c, L, grad, row0, nrows, lin, lr, clamp, step);
+}
+
+int sk_apply_vector_update(sk_ctx *c, const sk_dense *L, const float *colsums, uint32_t batch_stat,
+                           const sk_optim *lin, const sk_optim *nrm, float lr, float clamp, uint32_t step) {
+    int rc = check_layer(c, L, true);
+    if (rc) return rc;
+    if (!colsums || !lin || !nrm) return fail(c, SK_ERR_NULL_POINTER, "column sums or optimiser pointer is NULL");
+    if (batch_stat == 0) return fail(c, SK_ERR_INVALID_BATCH_SIZE, "Batch size must be more than zero.");
+    if (lin->kind > 1 || nrm->kind > 1) return fail(c, SK_ERR_INVALID_CONFIGURATION, "optimiser ordinal out of range");
+    return SK_DISPATCH(L->dtype, apply_vector_update_impl, c, L, colsums, batch_stat, lin, nrm, lr, clamp, step);
 }
 
 int sk_cast(sk_ctx *c, const void *src, uint32_t sd, void *dst, uint32_t dd, size_t len) {

@@ -362,4 +362,29 @@ struct EpiStoreF32 {
     }
 };
 
+// ---- scaled store in the storage type (16-bit gradient payload of the data-parallel exchange) ----
+template <typename T> struct EpiStoreScaled {
+    T *c;
+    uint32_t N;
+    float scale;
+    bool vec_ok;
+    template <int V>
+    __device__ __forceinline__ void run(uint32_t row, uint32_t col0, const float (&acc)[V], uint32_t ncols) const {
+        const size_t idx = (size_t)row * N + col0;
+        float v[V];
+#pragma unroll
+        for (int j = 0; j < V; ++j) v[j] = acc[j] * scale;
+        if (vec_ok && ncols == V) store_run<T, V>(c + idx, true, v);
+        else for (uint32_t j = 0; j < ncols; ++j) c[idx + j] = from_f32<T>(v[j]);
+    }
+
+    struct Cols {};
+    using Pre = NoPre;
+    __device__ __forceinline__ void cols(uint32_t, Cols &) const {}
+    __device__ __forceinline__ void prefetch(uint32_t, uint32_t, Pre &) const {}
+    __device__ __forceinline__ void finish(uint32_t row, uint32_t col0, const float (&acc)[8], const Pre &, const Cols &) const {
+        run<8>(row, col0, acc, 8);
+    }
+};
+
 } // namespace sk

@@ -387,6 +387,40 @@ weight_update_kernel(const float *__restrict__ dw, T *w, float *master, float *d
     }
 }
 
+// Weight step on a contiguous range of elements from a gradient stored as G (f32 or the
+// 16-bit storage type), already averaged over the batch: g = grad * grad_scale (the remaining
+// loss-scale factor). Used by the sharded data-parallel update, where each rank steps 1/W of
+// every weight matrix.
+template <typename T, typename G>
+__global__ void __launch_bounds__(kRowThreads)
+weight_update_range_kernel(const G *__restrict__ grad, float grad_scale, T *w, float *master, float *dv, float *dm,
+                           size_t len, Optim opt, Hyper hyp, bool vec_ok) {
+    constexpr int V = 8;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    if (vec_ok) {
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < len / V; i += stride) {
+            float g[V], p[V], v[V], m[V];
+            load_run<G, V>(grad + i * V, true, g);
+            load_run<float, V>(master + i * V, true, p);
+            load_run<float, V>(dv + i * V, true, v);
+            load_run<float, V>(dm + i * V, true, m);
+#pragma unroll
+            for (int j = 0; j < V; ++j) p[j] = optimiser_step_fast(p[j], v[j], m[j], g[j] * grad_scale, opt, hyp, true);
+            store_run<float, V>(dv + i * V, true, v);
+            store_run<float, V>(dm + i * V, true, m);
+            store_run<float, V>(master + i * V, true, p);
+            if ((void *)w != (void *)master) store_run<T, V>(w + i * V, true, p);
+        }
+    } else {
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < len; i += stride) {
+            float v = dv[i], m = dm[i];
+            const float p = optimiser_step_fast(master[i], v, m, to_f32(grad[i]) * grad_scale, opt, hyp, true);
+            dv[i] = v; dm[i] = m; master[i] = p;
+            if ((void *)w != (void *)master) w[i] = from_f32<T>(p);
+        }
+    }
+}
+
 // util.cuh:9-19 casts and math.cuh:69-73 fill, grid-stride.
 template <typename S, typename D>
 __global__ void cast_kernel(const S *__restrict__ src, D *__restrict__ dst, size_t len) {

@@ -154,3 +154,20 @@ class GpuContext:
         self._check(self.lib.sk_apply_update(self.handle, C.byref(layer.desc()), dw.data_ptr(), colsums.data_ptr(),
                                              batch_stat, C.byref(lin), C.byref(nrm), train_ctx.learn_rate,
                                              train_ctx.grad_clamp, step & 0xFFFFFFFF))
+
+    def gpu_backward_grads_lp(self, layer, input: Tensor, batch_size: int, batch_stat: int, grad: torch.Tensor,
+                              colsums: torch.Tensor):
+        self._check(self.lib.sk_backward_grads_lp(self.handle, C.byref(layer.desc()), input.ptr(), input.rows(),
+                                                  batch_size, batch_stat, grad.data_ptr(), colsums.data_ptr()))
+
+    def gpu_apply_update_rows(self, layer, grad: torch.Tensor, row0: int, nrows: int, train_ctx, step: int):
+        lin = _optim(train_ctx.optimiser)
+        self._check(self.lib.sk_apply_update_rows(self.handle, C.byref(layer.desc()), grad.data_ptr(), row0, nrows,
+                                                  C.byref(lin), train_ctx.learn_rate, train_ctx.grad_clamp,
+                                                  step & 0xFFFFFFFF))
+
+    def gpu_apply_vector_update(self, layer, colsums: torch.Tensor, batch_stat: int, train_ctx, step: int):
+        lin, nrm = _optim(train_ctx.optimiser), _optim(train_ctx.norm_optimiser)
+        self._check(self.lib.sk_apply_vector_update(self.handle, C.byref(layer.desc()), colsums.data_ptr(), batch_stat,
+                                                    C.byref(lin), C.byref(nrm), train_ctx.learn_rate,
+                                                    train_ctx.grad_clamp, step & 0xFFFFFFFF))

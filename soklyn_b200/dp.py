@@ -8,6 +8,16 @@ order per layer is: local batch sums -> all-reduce (NCCL) -> optimiser step -> d
 layer below. Dropout hashes the global row index and every 1/M uses the global batch, so N
 ranks reproduce the single-device result up to the order of the f32 sums.
 
+Two exchange schemes:
+
+* "allreduce": f32 dW and column sums are all-reduced, every rank runs the whole optimiser step.
+* "sharded" (default for 16-bit blocks whose row count divides by the rank count): dW is produced
+  in the storage type, already averaged, and reduce-scattered by rows; each rank steps only its
+  1/W of the rows (f32 master, moments, 16-bit copy), then the 16-bit weights are all-gathered in
+  place. This halves the bytes on NVLink and divides the optimiser's HBM traffic by W. The f32
+  master weights and moments of a rank are then current only for the rows it owns
+  (`owned_rows(i)`); the 16-bit weights are complete everywhere.
+
 BatchNorm layers would need their column statistics all-reduced as well; that is not built.
 """
 from __future__ import annotations
@@ -33,7 +43,8 @@ def shard_rows(global_batch: int, rank: int, world: int):
 
 
 class DataParallelFFN:
-    def __init__(self, context, network: FeedForwardNetwork, global_batch: int, rank: int, world: int, group=None):
+    def __init__(self, context, network: FeedForwardNetwork, global_batch: int, rank: int, world: int, group=None,
+                 scheme: str = "auto"):
         self.ctx, self.net, self.group = context, network, group
         self.rank, self.world, self.global_batch = rank, world, global_batch
         self.row_offset, self.local_batch = shard_rows(global_batch, rank, world)
@@ -42,10 +53,31 @@ class DataParallelFFN:
                 raise log.InvalidConfiguration("BatchNorm is not supported under data parallelism")
         dev = context.device
         layers = network.get_layers() if world > 1 else []
-        self.dw = [torch.empty(l.get_weights().rows(), l.get_weights().cols(), device=dev, dtype=torch.float32)
-                   for l in layers]
+        self.sharded = []
+        self.dw, self.dw_shard = [], []
+        for l in layers:
+            k, n = l.get_weights().rows(), l.get_weights().cols()
+            can_shard = getattr(l, "precision", None) is not None and l.precision.value != 0 and k % world == 0
+            use = scheme == "sharded" or (scheme == "auto" and can_shard)
+            if use and not can_shard:
+                raise log.InvalidConfiguration("sharded exchange needs 16-bit blocks whose rows divide by the rank count")
+            self.sharded.append(use)
+            if use:
+                dt = l.get_weights().data.dtype
+                self.dw.append(torch.empty(k, n, device=dev, dtype=dt))
+                self.dw_shard.append(torch.empty(k // world, n, device=dev, dtype=dt))
+            else:
+                self.dw.append(torch.empty(k, n, device=dev, dtype=torch.float32))
+                self.dw_shard.append(None)
         self.colsums = [torch.empty(3, l.get_weights().cols(), device=dev, dtype=torch.float32) for l in layers]
         self.collectives = 0
+
+    def owned_rows(self, i: int):
+        """(first row, row count) of layer i's weight matrix whose master weights and moments this rank keeps current."""
+        k = self.net.get_layers()[i].get_weights().rows()
+        if self.world > 1 and self.sharded[i]:
+            return self.rank * (k // self.world), k // self.world
+        return 0, k
 
     def forward(self, input: Tensor, use_dropout: bool, step: int):
         return self.net.forward(self.ctx, input, self.local_batch, use_dropout, step, self.row_offset)
@@ -75,7 +107,18 @@ class DataParallelFFN:
                 tc1 = train_ctx.get_train_context(i)
                 self.ctx.gpu_backward_pass(layer, x, tc1, step)
                 continue
+            tci = train_ctx.get_train_context(i)
+            if self.sharded[i]:
+                self.ctx.gpu_backward_grads_lp(layer, x, self.local_batch, self.global_batch, self.dw[i], self.colsums[i])
+                dist.reduce_scatter_tensor(self.dw_shard[i], self.dw[i], group=self.group)
+                dist.all_reduce(self.colsums[i], group=self.group)
+                row0, nrows = self.owned_rows(i)
+                self.ctx.gpu_apply_update_rows(layer, self.dw_shard[i], row0, nrows, tci, step)
+                self.ctx.gpu_apply_vector_update(layer, self.colsums[i], self.global_batch, tci, step)
+                w = layer.get_weights().data
+                dist.all_gather_into_tensor(w, w[row0:row0 + nrows], group=self.group)
+                self.collectives += 3
+                continue
             self.ctx.gpu_backward_grads(layer, x, self.local_batch, self.dw[i], self.colsums[i])
             self._exchange(i)
-            self.ctx.gpu_apply_update(layer, self.dw[i], self.colsums[i], self.global_batch,
-                                      train_ctx.get_train_context(i), step)
+            self.ctx.gpu_apply_update(layer, self.dw[i], self.colsums[i], self.global_batch, tci, step)

@@ -1,0 +1,83 @@
+"""Data-parallel parity on real GPUs, run under torchrun (one rank per GPU):
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 tests/dp_check.py
+
+Every rank trains its row shard of a seeded batch for a few steps with DataParallelFFN; rank 0
+also trains the whole batch on one device and requires the data-parallel weights, outputs and
+dropout masks to agree with it (16-bit rule of tests/harness.py for Adam-updated parameters).
+Exercised by tests/test_dp_gpu.py when two GPUs are visible."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+
+def main():
+    import harness as H
+    import soklyn_b200 as sk
+    from soklyn_b200 import configs
+    from soklyn_b200.core import Tensor, reset_tensor_ids
+    from soklyn_b200.dp import DataParallelFFN
+    rank, local, world = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ctx = sk.GpuContext(16, local)
+    steps = 3
+    specs = [configs.scaled(configs.CONFIGS[4], dims=(256, 512, 256, 512, 256), batch=256, name="dp_sharded_f16"),
+             configs.scaled(configs.CONFIGS[3], dims=(384, 256, 128, 16), batch=128, name="dp_dropout_layernorm_f16"),
+             configs.scaled(configs.CONFIGS[1], dims=(96, 64, 32, 10), batch=64, name="dp_allreduce_f32")]
+    ok = True
+    for spec in specs:
+        w = configs.make_weights(spec)
+        x, t, _ = configs.make_data(spec)
+        per = spec.batch // world
+        reset_tensor_ids(0)
+        net = configs.build_network(ctx, spec, w, max_batch=per)
+        dp = DataParallelFFN(ctx, net, spec.batch, rank, world)
+        xs = Tensor.from_cpu_vector(ctx, x[rank * per:(rank + 1) * per], (per, spec.dims[0]), spec.prec())
+        ts = Tensor.from_cpu_vector(ctx, t[rank * per:(rank + 1) * per], (per, spec.dims[-1]), spec.prec())
+        lrs = H.lr_schedule(spec, steps)
+        for s in range(1, steps + 1):
+            outs = dp.forward(xs, spec.use_dropout, s)
+            dp.backward(outs, ts, xs, spec.loss_config(), spec.train_context(lr=lrs[s - 1]), s)
+        ctx.synchronize()
+        # every rank holds the same 16-bit / f32 weights afterwards
+        for i, layer in enumerate(net.get_layers()):
+            wt = layer.get_weights().data.float()
+            ref = wt.clone()
+            dist.broadcast(ref, 0)
+            assert torch.equal(wt, ref), f"{spec.name}: layer {i} weights differ between ranks"
+        if rank == 0:
+            single, _ = H.run_device(ctx, spec, w, x, t, steps)
+            tol = 1e-2 if spec.precision != "f32" else 5e-4
+            for i, (a, b) in enumerate(zip(net.get_layers(), single.get_layers())):
+                wa, wb = a.get_weights().download(ctx).astype(np.float64), b.get_weights().download(ctx).astype(np.float64)
+                moved = np.abs(wa - wb) / max(lrs)
+                rel = H.relerr(wa, wb)
+                if spec.optimiser == "adam":
+                    good = rel <= tol or ((moved > 0.1 * steps).mean() <= 0.02 and moved.max() <= 2.5 * steps)
+                else:
+                    good = rel <= tol
+                oa, ob = a.get_outputs().download(ctx)[:per].astype(np.float64), b.get_outputs().download(ctx)[:per].astype(np.float64)
+                rel_o = H.relerr(oa, ob)
+                ma, mb = a.get_masks().download(ctx)[:per], b.get_masks().download(ctx)[:per]
+                mask_ok = np.array_equal(ma != 0, mb != 0)
+                print(f"{spec.name} L{i}: weights rel {rel:.2e} (max moved {moved.max():.2f} lr), outputs rel {rel_o:.2e}, "
+                      f"masks {'equal' if mask_ok else 'DIFFER'}, sharded={dp.sharded[i]}", flush=True)
+                ok = ok and good and mask_ok and rel_o <= 5 * tol
+    flag = torch.tensor([1 if ok else 0], device=ctx.device)
+    dist.broadcast(flag, 0)
+    dist.destroy_process_group()
+    if rank == 0:
+        print("DP_CHECK_OK" if ok else "DP_CHECK_FAILED", flush=True)
+    sys.exit(0 if int(flag.item()) == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()
