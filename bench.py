@@ -157,14 +157,21 @@ def run_ours(args):
         dp.backward(outs, td, xd, lc, tc, s)
 
     out_host = torch.empty((local, spec.dims[-1]), dtype=tdt).pin_memory()
+    from soklyn_b200.pipeline import HostFeeder
+    feeder = HostFeeder(ctx, [tuple(x_host.shape), tuple(t_host.shape)], prec)
+    feeder.stage(1, [x_host, t_host])   # the first step (s = 1) reads slot 1
 
     def step_e2e(s):
-        xs = Tensor.from_cpu_vector(ctx, x_host, x_host.shape, prec)
-        ts = Tensor.from_cpu_vector(ctx, t_host, t_host.shape, prec)
+        # inputs of this step were staged from pinned host memory during the previous one; the
+        # next step's are staged now; the output goes back to the host while backward runs
+        slot = s % 2
+        xs, ts = feeder.acquire(slot)
+        feeder.stage(1 - slot, [x_host, t_host])
         outs = dp.forward(xs, spec.use_dropout, s)
-        out_host.copy_(outs[-1].data[:local], non_blocking=True)
+        feeder.fetch(outs[-1], out_host, local)
         dp.backward(outs, ts, xs, lc, tc, s)
-        torch.cuda.current_stream().synchronize()   # the step's result is on the host
+        feeder.release(slot)
+        feeder.wait_output()                        # the step's result is on the host
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -180,7 +187,8 @@ def run_ours(args):
     clocks = sampler.stop() if rank == 0 else None
     prof = ctx.profile_read()   # per-kernel-class device time inside the timed region
     ctx.profile_enable(False)
-    ms_e2e = timed_steps(step_e2e, args.steps, 1, world, device)
+    # the e2e warm-up must leave slot parity consistent: step numbers continue from the warm-up
+    ms_e2e = timed_steps(step_e2e, args.steps, 2, world, device)
 
     if rank == 0:
         peaks = measured_peaks()
@@ -221,6 +229,74 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_gemm_sweep(args):
+    """BASELINE config 5: the three GEMMs of one DenseBlock in isolation, with their fused epilogues,
+    over M x K x N (forward with bias + activation, dX with the activation-derivative / mask epilogue,
+    dW with the column sums and the fused optimiser step). X, W, dY ~ N(0,1)/sqrt(K), seeded."""
+    import soklyn_b200 as sk
+    from soklyn_b200.configs import _GivenWeights
+    from soklyn_b200.core import Tensor
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    ctx = sk.GpuContext(16, 0)
+    peaks = measured_peaks()
+    acts = [sk.Activation.ReLU, sk.Activation.SiLU, sk.Activation.Tanh]
+    ms_list = [int(v) for v in args.sweep_m.split(",")]
+    kn_list = [int(v) for v in args.sweep_kn.split(",")]
+    rows, idx = [], 0
+    for prec_name in args.sweep_dtypes.split(","):
+        prec = {"f16": sk.Precision.FP16, "f32": sk.Precision.FP32, "bf16": sk.Precision.BF16}[prec_name]
+        for m in ms_list:
+            for k in kn_list:
+                for n in kn_list:
+                    if prec_name == "f32" and float(m) * k * n > 2.8e11:
+                        continue   # the FFMA path at these sizes takes seconds per call
+                    gen = torch.Generator(device="cpu").manual_seed(5000 + idx)
+                    act = acts[idx % 3]
+                    idx += 1
+                    w = (torch.randn(k, n, generator=gen) / k ** 0.5).numpy()
+                    cfg = sk.LayerInitConfig(sk.Normalisation.Disabled, act, sk.Regularisation.none(), 0.0)
+                    blk = sk.DenseBlock(ctx, True, k, n, m, _GivenWeights(w), cfg, prec)
+                    nxt = sk.DenseBlock(ctx, True, n, k, m, _GivenWeights(w.T.copy()), sk.LayerInitConfig(), prec)
+                    x = Tensor.from_cpu_vector(ctx, (torch.randn(m, k, generator=gen) / k ** 0.5).numpy(), (m, k), prec)
+                    dy = torch.randn(m, k, generator=gen) / k ** 0.5
+                    nxt.get_delta_prenorm_out().data.copy_(dy)
+                    if nxt.d_prenorm_lp is not None:
+                        nxt.d_prenorm_lp.data.copy_(dy)
+                    tc = sk.TrainContext(sk.Optimiser.Adam(), sk.Optimiser.Adam(), m, 1e-3)
+                    ops = {"forward": lambda: blk.forward(ctx, x, m, False, 1),
+                           "dX": lambda: ctx.gpu_hidden_layer_error(blk, nxt, m),
+                           "dW": lambda: ctx.gpu_backward_pass(blk, x, tc, 1)}
+                    rec = {"dtype": prec_name, "M": m, "K": k, "N": n, "act": act.ordinal()}
+                    for name, fn in ops.items():
+                        for _ in range(3):
+                            fn()
+                        torch.cuda.synchronize()
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        iters = 5 if float(m) * k * n < 1e12 else 2
+                        e0.record()
+                        for _ in range(iters):
+                            fn()
+                        e1.record()
+                        torch.cuda.synchronize()
+                        ms = e0.elapsed_time(e1) / iters
+                        rec[name + "_ms"] = round(ms, 4)
+                        rec[name + "_tflops"] = round(2.0 * m * k * n / (ms * 1e-3) / 1e12, 1)
+                    rows.append(rec)
+                    del blk, nxt, x
+                    torch.cuda.empty_cache()
+    big = [r for r in rows if r["dtype"] != "f32" and r["M"] >= 4096]
+    best = max((r["forward_tflops"] for r in big), default=0.0)
+    mean = sum(r["forward_tflops"] + r["dX_tflops"] + r["dW_tflops"] for r in big) / max(1, 3 * len(big))
+    line = {"metric": "DenseBlock GEMM TFLOP/s", "value": mean, "unit": "TFLOP/s", "n_gpus": 1, "steps": 1, "warmup": 3,
+            "higher_is_better": True, "dtype": args.sweep_dtypes, "data": "synthetic (seeded N(0,1)/sqrt(K))",
+            "config": {"workload": "dense_block_gemm_sweep", "M": ms_list, "KN": kn_list,
+                       "note": "value = mean over forward/dX/dW of the 16-bit cases with M >= 4096, fused epilogues included"},
+            "best_forward_tflops": best, "peak": peaks["tflops"], "frac_of_peak": mean / peaks["tflops"], "sweep": rows}
+    print(json.dumps(line), flush=True)
+    ctx.close()
+
+
 def run_reference(args):
     """The reference's own kernels (oracle/_ref: its unmodified nn_math.cu, JIT-ed from compute_75 PTX as its
     build.rs targets) with its launch configuration and per-launch stream synchronisation, on a bounded
@@ -229,7 +305,7 @@ def run_reference(args):
     if rank != 0:
         return
     from soklyn_b200 import configs
-    spec = configs.CONFIGS[args.config]
+    spec = configs.CONFIGS[args.config if args.config in configs.CONFIGS else 4]
     rows = args.ref_rows
     sample = configs.scaled(spec, batch=rows)
     from oracle import ref_kernels
@@ -288,8 +364,13 @@ def main():
     ap.add_argument("--cpu-rows", type=int, default=256, help="rows of the batch the CPU baseline leg runs")
     ap.add_argument("--ref-rows", type=int, default=256, help="rows of the batch the reference arm runs per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sweep-m", default="256,1024,4096,16384,65536")
+    ap.add_argument("--sweep-kn", default="1024,4096,8192")
+    ap.add_argument("--sweep-dtypes", default="f16,f32")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.config == 5 and args.impl != "reference":
+        run_gemm_sweep(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

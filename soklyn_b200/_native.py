@@ -133,7 +133,8 @@ def exported_symbols() -> list[str]:
 def lib() -> C.CDLL:
     global _lib
     if _lib is None:
-        path = _LIB if os.path.exists(_LIB) and not _stale() else build()
+        # SOKLYN_B200_LIB points at an alternative build of the same library (kernel experiments)
+        path = os.environ.get("SOKLYN_B200_LIB") or (_LIB if os.path.exists(_LIB) and not _stale() else build())
         _lib = C.CDLL(path)
         for name, (res, args) in _SIGS.items():
             fn = getattr(_lib, name)  # AttributeError here = the library lacks a declared symbol

@@ -42,6 +42,18 @@ template <int BN> struct TcShape {
 
 enum : int { kTcErrProducer = 1, kTcErrMma = 2, kTcErrEpilogue = 3 };
 
+// Tile order. Tiles are walked in groups of kTcGroupN tile-columns, row-major inside a group, so
+// that the ~148 tiles in flight form a compact block (about 18 x 8 tiles): the B panels of a group
+// stay in L2 while A streams past once per group, instead of once per tile-column.
+constexpr uint32_t kTcGroupN = 8;
+__device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uint32_t tiles_n, uint32_t &mi, uint32_t &ni) {
+    const uint32_t group_tiles = kTcGroupN * tiles_m;
+    const uint32_t g = tile / group_tiles, r = tile - g * group_tiles;
+    const uint32_t width = min(kTcGroupN, tiles_n - g * kTcGroupN);
+    mi = r / width;
+    ni = g * kTcGroupN + (r - mi * width);
+}
+
 template <bool A_MN, bool B_MN, int BN, class Epi>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -84,7 +96,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int32_t m0 = (tile % tiles_m) * kTcBM, n0 = (tile / tiles_m) * BN;
+                uint32_t mi, ni;
+                tile_coords(tile, tiles_m, tiles_n, mi, ni);
+                const int32_t m0 = mi * kTcBM, n0 = ni * BN;
                 for (uint32_t kb = 0; kb < num_kb; ++kb) {
                     if (!tc::mbar_wait(&empty_bar[stage], phase ^ 1)) { ok = false; break; }
                     tc::mbar_arrive_expect_tx(&full_bar[stage], S::kStageBytes);
@@ -146,7 +160,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
         for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-            const uint32_t m0 = (tile % tiles_m) * kTcBM, n0 = (tile / tiles_m) * BN;
+            uint32_t mi, ni;
+            tile_coords(tile, tiles_m, tiles_n, mi, ni);
+            const uint32_t m0 = mi * kTcBM, n0 = ni * BN;
             if (!tc::mbar_wait(&tmem_full[acc], acc_phase)) { ok = false; break; }
             tc::tc_fence_after_sync();
 #pragma unroll 1
