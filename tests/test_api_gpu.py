@@ -1,0 +1,181 @@
+"""Error behaviour of the drop-in API (the checks of src/mlp.rs and src/io/device.rs), status codes
+of the C ABI called directly, checkpoint round trip, and the utility kernels."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+import harness as H
+import soklyn_b200 as sk
+from soklyn_b200 import _native, configs, log
+from soklyn_b200.configs import _GivenWeights
+
+pytestmark = pytest.mark.gpu
+
+
+def _block(ctx, k=12, n=8, batch=6, training=True, prec=sk.Precision.FP32, cfg=None):
+    w = np.random.default_rng(3).standard_normal((k, n)).astype(np.float32) * 0.1
+    return sk.DenseBlock(ctx, training, k, n, batch, _GivenWeights(w), cfg or sk.LayerInitConfig(), prec)
+
+
+def _x(ctx, rows, cols, prec=sk.Precision.FP32):
+    return sk.Tensor.from_cpu_vector(ctx, np.ones((rows, cols), np.float32), (rows, cols), prec)
+
+
+def test_constructor_and_forward_checks(gpu_ctx):
+    with pytest.raises(log.InvalidConfiguration):
+        sk.DenseBlock(gpu_ctx, True, 0, 4, 4, sk.InitZeroFunc())
+    with pytest.raises(log.InvalidConfiguration):
+        sk.DenseBlock(gpu_ctx, True, 4, 4, 0, sk.InitZeroFunc())
+    blk = _block(gpu_ctx)
+    with pytest.raises(log.MismatchedDimensions):
+        blk.forward(gpu_ctx, _x(gpu_ctx, 4, 12), 5, False, 1)           # fewer rows than the batch
+    with pytest.raises(log.AllocationLimitExceeded):
+        blk.forward(gpu_ctx, _x(gpu_ctx, 7, 12), 6, False, 1)           # more rows than max_batch
+    with pytest.raises(log.MismatchedDimensions):
+        blk.forward(gpu_ctx, _x(gpu_ctx, 6, 11), 6, False, 1)           # wrong feature count
+    with pytest.raises(log.InvalidBatchSize):
+        blk.forward(gpu_ctx, _x(gpu_ctx, 6, 12), 0, False, 1)
+    blk.set_activation(sk.Activation.Softmax)
+    with pytest.raises(log.InvalidConfiguration):
+        blk.forward(gpu_ctx, _x(gpu_ctx, 6, 12), 6, False, 1)
+    blk.set_activation(sk.Activation.ReLU)
+    blk.set_normalisation(sk.Normalisation.BatchNorm)
+    with pytest.raises(log.InvalidBatchSize):
+        blk.forward(gpu_ctx, _x(gpu_ctx, 6, 12), 1, False, 1)
+    assert blk.forward(gpu_ctx, _x(gpu_ctx, 6, 12), 6, False, 1) is blk.get_outputs()
+
+
+def test_backward_and_loss_checks(gpu_ctx):
+    inf = _block(gpu_ctx, training=False)
+    tc = sk.TrainContext(sk.Optimiser.SGD(), sk.Optimiser.SGD(), 6, 0.1)
+    with pytest.raises(log.TrainingModeRequired):
+        inf.backward_output(gpu_ctx, _x(gpu_ctx, 6, 12), tc, 1)
+    with pytest.raises(log.TrainingModeRequired):
+        inf.compute_loss(gpu_ctx, _x(gpu_ctx, 6, 8), sk.LossConfig(sk.LossFunc.MeanSquareLoss, sk.Activation.Identity))
+    blk = _block(gpu_ctx)
+    with pytest.raises(log.MismatchedDimensions):
+        blk.compute_loss(gpu_ctx, _x(gpu_ctx, 6, 7), sk.LossConfig(sk.LossFunc.MeanSquareLoss, sk.Activation.Identity))
+    with pytest.raises(log.AllocationLimitExceeded):
+        blk.compute_loss(gpu_ctx, _x(gpu_ctx, 9, 8), sk.LossConfig(sk.LossFunc.MeanSquareLoss, sk.Activation.Identity))
+    for lf, act in ((sk.LossFunc.MeanSquareLoss, sk.Activation.Softmax), (sk.LossFunc.CrossEntropyLoss, sk.Activation.Sigmoid),
+                    (sk.LossFunc.BinaryCrossEntropy, sk.Activation.Softmax)):
+        with pytest.raises(log.InvalidConfiguration):
+            blk.compute_loss(gpu_ctx, _x(gpu_ctx, 6, 8), sk.LossConfig(lf, act))
+    nxt = _block(gpu_ctx, k=9, n=4)                                       # 9 rows do not follow 8 columns
+    with pytest.raises(log.MismatchedDimensions):
+        blk.backward_hidden(gpu_ctx, nxt, _x(gpu_ctx, 6, 12), tc, 1)
+    net = sk.FeedForwardNetwork([blk], 12)
+    with pytest.raises(log.InvalidConfiguration):
+        net.backward(gpu_ctx, [], _x(gpu_ctx, 6, 8), _x(gpu_ctx, 6, 12),
+                     sk.LossConfig(sk.LossFunc.MeanSquareLoss, sk.Activation.Identity),
+                     sk.MultiLayerTrainContext([sk.Optimiser.SGD()], [sk.Optimiser.SGD()], 6, 0.1), 1)
+    with pytest.raises(log.InvalidConfiguration):
+        sk.FeedForwardNetwork([], 12).forward_raw(gpu_ctx, np.zeros(12, np.float32), 1, False, 1)
+
+
+def test_sixteen_bit_needs_tile_dim_16():
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    ctx32 = sk.GpuContext(32, 0)
+    try:
+        blk = _block(ctx32, prec=sk.Precision.FP16)
+        with pytest.raises(log.HardwareConstraintViolation):
+            blk.forward(ctx32, _x(ctx32, 6, 12, sk.Precision.FP16), 6, False, 1)
+        f32 = _block(ctx32)
+        f32.forward(ctx32, _x(ctx32, 6, 12), 6, False, 1)               # f32 accepts tile 32
+    finally:
+        ctx32.close()
+
+
+def test_c_abi_status_codes(gpu_ctx):
+    lib = _native.lib()
+    blk = _block(gpu_ctx)
+    d = blk.desc()
+    x = _x(gpu_ctx, 6, 12)
+    h = gpu_ctx.handle
+    assert lib.sk_dense_forward(h, C.byref(d), x.ptr(), 6, 6, 0, 1, 0) == 0
+    assert lib.sk_dense_forward(h, C.byref(d), x.ptr(), 4, 6, 0, 1, 0) == 2      # MismatchedDimensions
+    assert lib.sk_dense_forward(h, C.byref(d), x.ptr(), 7, 6, 0, 1, 0) == 3      # AllocationLimitExceeded
+    assert lib.sk_dense_forward(h, C.byref(d), x.ptr(), 6, 0, 0, 1, 0) == 5      # InvalidBatchSize
+    assert lib.sk_dense_forward(h, C.byref(d), None, 6, 6, 0, 1, 0) == 9         # NULL input
+    assert b"Batch size" in lib.sk_last_error(h) or b"NULL" in lib.sk_last_error(h)
+    bad = type(d)()
+    C.memmove(C.byref(bad), C.byref(d), C.sizeof(d))
+    bad.act = 5
+    assert lib.sk_dense_forward(h, C.byref(bad), x.ptr(), 6, 6, 0, 1, 0) == 4    # Softmax in forward
+    bad.act, bad.is_training = 0, 0
+    lin = _native.SkOptim(0, 0.0, 0.0, 0.0, 0)
+    assert lib.sk_backward_update(h, C.byref(bad), x.ptr(), 6, 6, C.byref(lin), C.byref(lin), 0.1, 1.0, 1) == 6
+    assert lib.sk_cast(h, x.ptr(), 0, x.ptr(), 0, 4) == 8                        # f32 -> f32 is not a cast
+    assert lib.sk_sync(h) == 0
+
+
+def test_checkpoint_round_trip(gpu_ctx, tmp_path):
+    from soklyn_b200.safetensor import SafetensorFile
+    spec = configs.scaled(configs.CONFIGS[4], dims=(64, 128, 64), batch=32, name="ckpt_f16")
+    w = configs.make_weights(spec)
+    x, t, _ = configs.make_data(spec)
+    net, _ = H.run_device(gpu_ctx, spec, w, x, t, 2)
+    f = SafetensorFile.from_ffn(gpu_ctx, net)
+    f.pass_metadata("epoch", 2)
+    path = os.path.join(tmp_path, "net.safetensors")
+    f.save(path)
+    back = SafetensorFile.read(path)
+    assert back.get_metadata() == {"epoch": "2"}
+    blocks = back.into_blocks(gpu_ctx, True, 32, sk.Precision.FP16)
+    assert len(blocks) == 2
+    for a, b in zip(net.get_layers(), blocks):
+        for getter in ("get_weights", "get_biases", "get_norm_weights", "get_master_weights", "get_dv_weights",
+                       "get_dm_weights", "get_dm_biases", "get_master_norm_weights"):
+            assert np.array_equal(getattr(a, getter)().download(gpu_ctx), getattr(b, getter)().download(gpu_ctx)), getter
+        assert b.get_normalisation() == sk.Normalisation.Disabled and b.get_activation() == sk.Activation.Identity
+    # a resumed network continues exactly like the original once its configuration is set again
+    for i, b in enumerate(blocks):
+        c = spec.layer_config(i)
+        b.set_normalisation(c.normalisation); b.set_activation(c.activation); b.set_mask_coeff(c.mask_coeff)
+    resumed = sk.FeedForwardNetwork(blocks, spec.dims[0])
+    xd = sk.Tensor.from_cpu_vector(gpu_ctx, x, x.shape, spec.prec())
+    o1 = net.forward(gpu_ctx, xd, spec.batch, False, 3)[-1].download(gpu_ctx)
+    o2 = resumed.forward(gpu_ctx, xd, spec.batch, False, 3)[-1].download(gpu_ctx)
+    assert np.array_equal(o1, o2)
+    inference = SafetensorFile.read(path).into_blocks(gpu_ctx, False, 32, sk.Precision.FP16)
+    assert inference[0].get_dv_weights() is None and not inference[0].is_training_mode()
+
+
+def test_cast_fill_and_reset_mask(gpu_ctx):
+    a = sk.Tensor.from_cpu_vector(gpu_ctx, np.linspace(-3, 3, 1001, dtype=np.float32), (1001,))
+    h = a.cast(gpu_ctx, sk.Precision.FP16)
+    assert np.array_equal(h.download(gpu_ctx), np.linspace(-3, 3, 1001, dtype=np.float32).astype(np.float16))
+    back = h.cast(gpu_ctx, sk.Precision.FP32)
+    assert np.array_equal(back.download(gpu_ctx), h.download(gpu_ctx).astype(np.float32))
+    with pytest.raises(log.UnsupportedTypeCast):
+        gpu_ctx.gpu_cast_t(a, back)
+    blk = _block(gpu_ctx, cfg=sk.LayerInitConfig(sk.Normalisation.Disabled, sk.Activation.ReLU, sk.Regularisation.none(), 0.5))
+    blk.forward(gpu_ctx, _x(gpu_ctx, 6, 12), 6, True, 1)
+    m = blk.get_masks().download(gpu_ctx)
+    assert set(np.unique(m)) <= {0.0, 2.0} and (m == 0).any()
+    blk.forward(gpu_ctx, _x(gpu_ctx, 6, 12), 6, False, 2)               # mask persists without dropout
+    assert np.array_equal(blk.get_masks().download(gpu_ctx), m)
+    blk.reset_mask(gpu_ctx)
+    assert (blk.get_masks().download(gpu_ctx) == 1).all()
+
+
+@pytest.mark.parametrize("prec", ["f16", "bf16"])
+def test_batchnorm_and_regularisation_sixteen_bit(gpu_ctx, prec):
+    """BatchNorm statistics, L2 regularisation and SGD-Nesterov through the 16-bit path against the f32 oracle."""
+    spec = configs.NetSpec(7, "bn_" + prec, (64, 96, 32), ("batch", "disabled"), ("tanh", "identity"), (0.0, 0.0), prec,
+                           "mse", "identity", "sgd", 0.05, 48, "xavier_normal", "normal", "normal")
+    w = configs.make_weights(spec)
+    x, t, _ = configs.make_data(spec)
+    if prec == "bf16":
+        import torch
+        rb = lambda a: torch.from_numpy(a).to(torch.bfloat16).float().numpy()
+        w, x, t = [rb(a) for a in w], rb(x), rb(t)
+    onet, oloss = H.run_oracle(spec, w, x, t, 1)
+    dnet, dloss = H.run_device(gpu_ctx, spec, w, x, t, 1)
+    tol = 1e-2 if prec == "f16" else 6e-2      # bf16 keeps 8 significant bits
+    H.compare_states(gpu_ctx, spec, dnet, onet, tol, skip=("mask",))
+    np.testing.assert_allclose(dloss, oloss, rtol=tol)
