@@ -151,6 +151,18 @@ int sk_backward_update(sk_ctx *ctx, const sk_dense *layer, const void *x, uint32
                        uint32_t batch, const sk_optim *linear, const sk_optim *norm_opt,
                        float learn_rate, float grad_clamp, uint32_t step);
 
+/* FeedForwardNetwork::forward (src/ffn.rs:40-57) and ::backward (src/ffn.rs:113-166) for a stack of
+ * blocks in one call: the same per-layer entry points in the reference's order (output layer
+ * first, every hidden delta after the next layer's update), sequenced in native code so that
+ * small networks are not bound by per-call host overhead. layers[i+1].K must equal layers[i].N;
+ * linear / norm_opt are arrays of n_layers optimisers. */
+int sk_ffn_forward(sk_ctx *ctx, const sk_dense *const *layers, uint32_t n_layers, const void *x, uint32_t x_rows,
+                   uint32_t batch, uint32_t use_dropout, uint32_t step, uint32_t row_offset);
+int sk_ffn_backward(sk_ctx *ctx, const sk_dense *const *layers, uint32_t n_layers, const void *target,
+                    uint32_t target_rows, const void *x, uint32_t x_rows, uint32_t loss, uint32_t loss_act,
+                    float loss_leaky, const sk_optim *linear, const sk_optim *norm_opt, uint32_t batch,
+                    float learn_rate, float grad_clamp, uint32_t step);
+
 /* The two halves of sk_backward_update, for data parallelism (no counterpart in the
  * reference, which is single-device): sk_backward_grads writes the raw batch sums
  * dW f32 [K x N] and colsums f32 [3 x N] (dB, sum dNorm_w, sum dNorm_b; still x512) so

@@ -46,6 +46,11 @@ class RefContext(GpuContext):
             raise RuntimeError("could not load the reference PTX module")
         self.ref.ref_configure(C.c_void_p(self.stream.cuda_stream), tile_dim, int(sync_each_launch))
 
+    # the whole-network calls of the product library must not be used: every layer goes through
+    # the reference kernels below
+    gpu_ffn_forward = None
+    gpu_ffn_backward = None
+
     def _rc(self, rc):
         if rc != 0:
             raise RuntimeError(f"reference kernel launch failed (status {rc})")

@@ -108,6 +108,11 @@ _SIGS = {
     "sk_hidden_error": (C.c_int, [C.c_void_p, C.POINTER(SkDense), C.POINTER(SkDense), C.c_uint32, C.c_uint32]),
     "sk_backward_update": (C.c_int, [C.c_void_p, C.POINTER(SkDense), C.c_void_p, C.c_uint32, C.c_uint32,
                                      C.POINTER(SkOptim), C.POINTER(SkOptim), C.c_float, C.c_float, C.c_uint32]),
+    "sk_ffn_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32,
+                                 C.c_uint32, C.c_uint32]),
+    "sk_ffn_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32,
+                                  C.c_uint32, C.c_uint32, C.c_float, C.c_void_p, C.c_void_p, C.c_uint32, C.c_float,
+                                  C.c_float, C.c_uint32]),
     "sk_backward_grads": (C.c_int, [C.c_void_p, C.POINTER(SkDense), C.c_void_p, C.c_uint32, C.c_uint32,
                                     C.c_void_p, C.c_void_p]),
     "sk_apply_update": (C.c_int, [C.c_void_p, C.POINTER(SkDense), C.c_void_p, C.c_void_p, C.c_uint32,

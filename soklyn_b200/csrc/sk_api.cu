@@ -597,7 +597,14 @@ uint64_t sk_launch_count(const sk_ctx *c) { return c ? c->launches : 0; }
 int sk_profile_enable(sk_ctx *c, int on) {
     if (!c) return SK_ERR_NULL_POINTER;
     c->profiling = on != 0;
-    if (on) c->ev_used = 0;
+    if (on) {
+        c->ev_used = 0;
+        while (c->ev_pool.size() < 2 * 1024) {   // create events now, not inside a timed region
+            cudaEvent_t a, b;
+            if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) break;
+            c->ev_pool.push_back(a); c->ev_pool.push_back(b); c->ev_class.push_back(0);
+        }
+    }
     return SK_OK;
 }
 
@@ -676,6 +683,51 @@ int sk_backward_update(sk_ctx *c, const sk_dense *L, const void *x, uint32_t x_r
     if ((rc = check_batch(c, L, x_rows, batch))) return rc;
     if (lin->kind > 1 || nrm->kind > 1) return fail(c, SK_ERR_INVALID_CONFIGURATION, "optimiser ordinal out of range");
     return SK_DISPATCH(L->dtype, backward_update_impl, c, L, x, batch, lin, nrm, lr, clamp, step);
+}
+
+int sk_ffn_forward(sk_ctx *c, const sk_dense *const *layers, uint32_t n, const void *x, uint32_t x_rows, uint32_t batch,
+                   uint32_t use_dropout, uint32_t step, uint32_t row_offset) {
+    if (!c || !layers) return SK_ERR_NULL_POINTER;
+    if (n == 0) return fail(c, SK_ERR_INVALID_CONFIGURATION, "Cannot execute a forward pass on an empty network");
+    const void *cur = x;
+    uint32_t rows = x_rows;
+    for (uint32_t i = 0; i < n; ++i) {
+        if (!layers[i]) return fail(c, SK_ERR_NULL_POINTER, "layer %u is NULL", i);
+        if (i > 0 && layers[i]->K != layers[i - 1]->N)
+            return fail(c, SK_ERR_MISMATCHED_DIMENSIONS, "forward input feature columns mismatch: expected %u, found %u",
+                        layers[i]->K, layers[i - 1]->N);
+        int rc = sk_dense_forward(c, layers[i], cur, rows, batch, use_dropout, step, row_offset);
+        if (rc) return rc;
+        cur = layers[i]->out;                 // the block's output tensor feeds the next block
+        rows = layers[i]->max_batch;
+    }
+    return SK_OK;
+}
+
+int sk_ffn_backward(sk_ctx *c, const sk_dense *const *layers, uint32_t n, const void *target, uint32_t target_rows,
+                    const void *x, uint32_t x_rows, uint32_t loss, uint32_t loss_act, float loss_leaky,
+                    const sk_optim *lin, const sk_optim *nrm, uint32_t batch, float lr, float clamp, uint32_t step) {
+    if (!c || !layers || !lin || !nrm) return SK_ERR_NULL_POINTER;
+    if (n == 0) return fail(c, SK_ERR_INVALID_CONFIGURATION, "Backward pass on an empty network");
+    for (uint32_t i = 0; i < n; ++i)
+        if (!layers[i]) return fail(c, SK_ERR_NULL_POINTER, "layer %u is NULL", i);
+    const uint32_t last = n - 1;
+    auto input_of = [&](uint32_t i, uint32_t &rows) -> const void * {
+        if (i == 0) { rows = x_rows; return x; }
+        rows = layers[i - 1]->max_batch;
+        return layers[i - 1]->out;
+    };
+    uint32_t rows = 0;
+    int rc = sk_output_error(c, layers[last], target, target_rows, layers[last]->max_batch, loss, loss_act, loss_leaky);
+    if (rc) return rc;
+    const void *in = input_of(last, rows);
+    if ((rc = sk_backward_update(c, layers[last], in, rows, batch, &lin[last], &nrm[last], lr, clamp, step))) return rc;
+    for (uint32_t i = last; i-- > 0;) {
+        if ((rc = sk_hidden_error(c, layers[i], layers[i + 1], batch, batch))) return rc;
+        in = input_of(i, rows);
+        if ((rc = sk_backward_update(c, layers[i], in, rows, batch, &lin[i], &nrm[i], lr, clamp, step))) return rc;
+    }
+    return SK_OK;
 }
 
 int sk_backward_grads(sk_ctx *c, const sk_dense *L, const void *x, uint32_t x_rows, uint32_t batch, float *dw,

@@ -171,3 +171,21 @@ class GpuContext:
         self._check(self.lib.sk_apply_vector_update(self.handle, C.byref(layer.desc()), colsums.data_ptr(), batch_stat,
                                                     C.byref(lin), C.byref(nrm), train_ctx.learn_rate,
                                                     train_ctx.grad_clamp, step & 0xFFFFFFFF))
+
+    # -- whole-network calls (src/ffn.rs sequencing done natively) --
+    def gpu_ffn_forward(self, layers, input: Tensor, batch_size: int, use_dropout: bool, step: int, row_offset: int = 0):
+        self.check_tile_dim(layers[0].precision)
+        ptrs = (C.c_void_p * len(layers))(*[C.addressof(l.desc()) for l in layers])
+        self._check(self.lib.sk_ffn_forward(self.handle, ptrs, len(layers), input.ptr(), input.rows(), batch_size,
+                                            int(use_dropout), step & 0xFFFFFFFF, row_offset))
+
+    def gpu_ffn_backward(self, layers, target: Tensor, input: Tensor, loss_config, train_ctx, step: int):
+        n = len(layers)
+        ptrs = (C.c_void_p * n)(*[C.addressof(l.desc()) for l in layers])
+        lin = (SkOptim * n)(*[_optim(o) for o in train_ctx.optimisers])
+        nrm = (SkOptim * n)(*[_optim(o) for o in train_ctx.norm_optimisers])
+        act = loss_config.activation
+        self._check(self.lib.sk_ffn_backward(self.handle, ptrs, n, target.ptr(), target.rows(), input.ptr(), input.rows(),
+                                             loss_config.loss_func.value, act.ordinal(), act.coeff, lin, nrm,
+                                             train_ctx.batch_size, train_ctx.learn_rate, train_ctx.grad_clamp,
+                                             step & 0xFFFFFFFF))

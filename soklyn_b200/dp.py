@@ -96,6 +96,9 @@ class DataParallelFFN:
             raise log.InvalidConfiguration(f"Backward pass expects exactly {n} activation vectors and optimizers.")
         if train_ctx.batch_size != self.global_batch:
             raise log.InvalidBatchSize("train context batch size must be the global batch")
+        if self.world == 1:   # nothing to exchange: the plain reference-order backward
+            self.net.backward(self.ctx, outputs, target, input, loss_config, train_ctx, step)
+            return
         last = n - 1
         layers[last].compute_loss(self.ctx, target, loss_config)
         for i in range(last, -1, -1):
