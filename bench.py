@@ -24,6 +24,14 @@ import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
 
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the three GEMM classes of the
+# default workload, from the ncu capture summarised in profiles/wide_ffn_step_ncu_full_b2048.md. That
+# capture ran the same network at batch 2048 (a full-size capture would hold too much device memory
+# for ncu's save/restore); the figures are its per-launch averages times 4, i.e. scaled by the rows
+# processed, which over-counts the weight operand (read once whatever the batch) by < 10 %.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {"gemm_forward": 4 * 292.5e6, "gemm_dx": 4 * 953.4e6, "gemm_dw": 4 * 1914.0e6}
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -109,18 +117,23 @@ def cpu_baseline_leg(spec, sample_rows: int):
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import harness as H
     from soklyn_b200 import configs
+    sample_rows = min(sample_rows, spec.batch)
     small = configs.scaled(spec, batch=sample_rows)
     w = configs.make_weights(small)
     x, t, _ = configs.make_data(small)
     net = H.build_oracle(small, w)
     opt = H._oracle_optim(small)
-    t0 = time.perf_counter()
-    outs = net.forward(x, small.batch, small.use_dropout, 1)
-    net.backward(outs, t, x, small.loss, small.loss_act, opt, opt, small.batch, small.lr, 1)
-    dt = time.perf_counter() - t0
+    steps, t0 = 0, time.perf_counter()
+    while True:       # at least one step; small networks repeat until about two seconds have passed
+        steps += 1
+        outs = net.forward(x, small.batch, small.use_dropout, steps)
+        net.backward(outs, t, x, small.loss, small.loss_act, opt, opt, small.batch, small.lr, steps)
+        dt = time.perf_counter() - t0
+        if dt > 2.0 or steps >= 2000:
+            break
     cores = len(os.sched_getaffinity(0))
-    return {"value": sample_rows / dt, "unit": "samples/s", "cores": cores, "kind": "port",
-            "sample": f"1 step on {sample_rows} of {spec.batch} rows (OpenMP, {cores} threads), {dt:.1f} s"}
+    return {"value": sample_rows * steps / dt, "unit": "samples/s", "cores": cores, "kind": "port",
+            "sample": f"{steps} step(s) on {sample_rows} of {spec.batch} rows (OpenMP, {cores} threads), {dt:.1f} s"}
 
 
 def run_ours(args):
@@ -227,7 +240,9 @@ def run_ours(args):
             "gpu_launches": int(launches),
             "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": peaks["tflops"],
-                         "unit": "TFLOP/s", "frac": achieved / peaks["tflops"], "traffic": None,
+                         "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get(top) if spec.cfg == 4 and world == 1 else None,
+                         "traffic_note": "bytes per launch, ncu capture at batch 2048 scaled x4 (see profiles/)",
                          "peak_source": peaks["source"] + " (bf16 matmul, sustained)",
                          "launches": int(n_l), "ms_per_launch": t_ms / max(1, n_l)},
             "kernel_ms_per_step": {k: v[1] / args.steps for k, v in prof.items()},
