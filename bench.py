@@ -153,7 +153,7 @@ def run_ours(args):
     ctx = sk.GpuContext(16, local_rank)
     local = spec.batch // world
     net = configs.build_network(ctx, spec, max_batch=local)
-    dp = DataParallelFFN(ctx, net, spec.batch, rank, world)
+    dp = DataParallelFFN(ctx, net, spec.batch, rank, world, scheme=args.dp_scheme)
     x, t, _ = configs.make_data(spec)
     r0 = rank * local
     prec = spec.prec()
@@ -230,7 +230,7 @@ def run_ours(args):
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": spec.precision, "data": "synthetic (seeded N(0,1) inputs/targets, Xavier-uniform weights)",
-            "config": {"workload": spec.name, "global_batch": spec.batch, "parallelism": f"dp{world}",
+            "config": {"workload": spec.name, "global_batch": spec.batch, "parallelism": f"dp{world}", "exchange": ("fused" if dp.fused else "nccl") if world > 1 else "none",
                        "params": spec.params(), "l2": "working set per step is far larger than L2 (126 MB)"},
             "tflops_per_step": spec.flops_per_step() / 1e12,
             "tflops_achieved": spec.flops_per_step() / (per_step * 1e-3) / 1e12,
@@ -250,6 +250,7 @@ def run_ours(args):
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_leg(spec, args.cpu_rows)
         print(json.dumps(line), flush=True)
+    dp.close()
     ctx.close()
     if world > 1:
         dist.destroy_process_group()
@@ -391,6 +392,8 @@ def main():
     ap.add_argument("--ref-rows", type=int, default=0,
                     help="rows of the batch the reference arm runs per step (0: 256 for config 4, the whole batch otherwise)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--dp-scheme", default="auto", choices=["auto", "fused", "sharded", "allreduce"],
+                    help="gradient exchange of the data-parallel runs (see soklyn_b200/dp.py)")
     ap.add_argument("--sweep-m", default="256,1024,4096,16384,65536")
     ap.add_argument("--sweep-kn", default="1024,4096,8192")
     ap.add_argument("--sweep-dtypes", default="f16,f32")

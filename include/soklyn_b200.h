@@ -187,6 +187,37 @@ int sk_apply_vector_update(sk_ctx *ctx, const sk_dense *layer, const float *cols
                            const sk_optim *linear, const sk_optim *norm_opt, float learn_rate, float grad_clamp,
                            uint32_t step);
 
+/* Fused form of the exchange for one process per GPU with peer-mapped buffers (no counterpart).
+ * Rank r owns rows [r*K/W, (r+1)*K/W) of each weight matrix and keeps a staging buffer
+ * T [W][K/W][N]. sk_backward_grads_scatter runs the dW GEMM and its epilogue stores every row block,
+ * averaged and in the storage type, into slot `rank` of the owner's staging buffer over NVLink
+ * (peer_stage[i] = staging buffer of rank i as mapped here). sk_signal_peers publishes a value in
+ * slot `slot` of every rank's flag array; sk_wait_flags waits (bounded: about two seconds, then
+ * SK_ERR_DEVICE_TIMEOUT at the next sk_sync) until all `world` slots of the local array reached it.
+ * sk_reduce_update_broadcast adds the W staged partials of the owned rows, steps them and writes the
+ * new 16-bit rows into row range `rank` of every rank's receive buffer T [K][N] (peer_w[i] = receive
+ * buffer of rank i), from where each rank copies them into its weight tensor after the second
+ * handshake. Staging, receive buffers and flag words live in the ranks' exchange arenas. */
+int sk_backward_grads_scatter(sk_ctx *ctx, const sk_dense *layer, const void *x, uint32_t x_rows, uint32_t batch,
+                              uint32_t batch_stat, void *const *peer_stage, uint32_t world, uint32_t rank,
+                              float *colsums);
+int sk_reduce_update_broadcast(sk_ctx *ctx, const sk_dense *layer, const void *stage, uint32_t world, uint32_t rank,
+                               void *const *peer_w, const sk_optim *linear, float learn_rate, float grad_clamp,
+                               uint32_t step);
+/* Exchange arena of one rank: sk_peer_alloc allocates `bytes` of zeroed device memory (set-up time,
+ * not the hot path) and returns a 64-byte CUDA IPC handle for it; the other ranks (other processes
+ * on the same node) turn that handle into a pointer usable by kernels of THEIR device with
+ * sk_peer_open, which maps it with this context's device current and peer access enabled.
+ * sk_peer_close / sk_peer_free undo them. */
+int sk_peer_alloc(sk_ctx *ctx, size_t bytes, void **ptr, unsigned char handle_out[64]);
+int sk_peer_open(sk_ctx *ctx, const unsigned char handle[64], void **ptr);
+int sk_peer_close(sk_ctx *ctx, void *ptr);
+int sk_peer_free(sk_ctx *ctx, void *ptr);
+/* Device-to-device copy of `bytes` on the context's stream (Tensor::clone, src/util/core.rs:686-692). */
+int sk_copy(sk_ctx *ctx, void *dst, const void *src, size_t bytes);
+int sk_signal_peers(sk_ctx *ctx, void *const *peer_flags, uint32_t world, uint32_t slot, uint32_t value);
+int sk_wait_flags(sk_ctx *ctx, const uint32_t *flags, uint32_t world, uint32_t value);
+
 /* No counterpart in the reference. Column sums over the batch of d_prenorm, d_norm_w and
  * d_norm_b, written to colsums f32 [3 x N] exactly as sk_backward_grads writes them, but
  * without a context and without allocating: for callers that are not allowed to allocate

@@ -123,6 +123,17 @@ _SIGS = {
                                        C.POINTER(SkOptim), C.c_float, C.c_float, C.c_uint32]),
     "sk_apply_vector_update": (C.c_int, [C.c_void_p, C.POINTER(SkDense), C.c_void_p, C.c_uint32, C.POINTER(SkOptim),
                                          C.POINTER(SkOptim), C.c_float, C.c_float, C.c_uint32]),
+    "sk_backward_grads_scatter": (C.c_int, [C.c_void_p, C.POINTER(SkDense), C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32,
+                                            C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p]),
+    "sk_reduce_update_broadcast": (C.c_int, [C.c_void_p, C.POINTER(SkDense), C.c_void_p, C.c_uint32, C.c_uint32,
+                                             C.c_void_p, C.POINTER(SkOptim), C.c_float, C.c_float, C.c_uint32]),
+    "sk_copy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "sk_peer_alloc": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p]),
+    "sk_peer_open": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p)]),
+    "sk_peer_close": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "sk_peer_free": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "sk_signal_peers": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32]),
+    "sk_wait_flags": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32]),
     "sk_column_sums_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32,
                                         C.c_uint32, C.c_uint32]),
     "sk_cast": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_size_t]),

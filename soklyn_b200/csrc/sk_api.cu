@@ -448,6 +448,47 @@ int apply_vector_update_impl(sk_ctx *c, const sk_dense *L, const float *colsums,
     return vector_update_launch<T>(c, L, colsums, 1, lin, nrm, hyp);
 }
 
+// dW GEMM whose epilogue scatters each row block to the staging buffer of the rank that owns it.
+template <typename T>
+int backward_grads_scatter_impl(sk_ctx *c, const sk_dense *L, const void *x, uint32_t batch, uint32_t batch_stat,
+                                void *const *peer_stage, uint32_t world, uint32_t rank, float *colsums) {
+    int rc = SK_OK;
+    const uint32_t nblocks = launch_colsum_partial(c, L, batch, &rc);
+    if (rc) return rc;
+    colsum_final_kernel<<<(3 * L->N + 255) / 256, 256, 0, c->stream>>>((const float *)c->workspace, colsums, L->N, nblocks);
+    c->launches++;
+    if ((rc = check_cuda(c, cudaGetLastError(), "column sums (final)"))) return rc;
+    EpiPeerScatter<T> epi{};
+    bool vec = L->N % 8 == 0;
+    for (uint32_t r = 0; r < world; ++r) { epi.stage[r] = (T *)peer_stage[r]; vec = vec && aligned16(peer_stage[r]); }
+    epi.rows_per_rank = L->K / world; epi.my_rank = rank; epi.N = L->N; epi.scale = 1.0f / (float)batch_stat; epi.vec_ok = vec;
+    ProfScope ps(c, SK_PROF_GEMM_DW);
+    rc = check_cuda(c, run_gemm<T, T, false, true>(c, L->dtype, (const T *)x, L->K, (const T *)L->d_prenorm_lp, L->N, L->K,
+                                                    L->N, batch, epi), "weight gradient gemm (scatter)");
+    c->launches++;
+    return rc;
+}
+
+template <typename T>
+int reduce_update_broadcast_impl(sk_ctx *c, const sk_dense *L, const void *stage, uint32_t world, uint32_t rank,
+                                 void *const *peer_w, const sk_optim *lin_, float lr, float clamp, uint32_t step) {
+    const Optim lin = make_optim(lin_, step);
+    const Hyper hyp{lr, clamp, 1.0f, L->regu, L->regu_coeff};   // the staged gradients are already averaged
+    const uint32_t rows = L->K / world;
+    const size_t off = (size_t)rank * rows * L->N, len = (size_t)rows * L->N;
+    PeerPtrs dst{};
+    for (uint32_t r = 0; r < world; ++r) dst.p[r] = (T *)peer_w[r] + off;
+    size_t blocks = (len / 8 + kRowThreads - 1) / kRowThreads;
+    const size_t cap = (size_t)c->num_sms * 8;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    ProfScope ps(c, SK_PROF_UPDATE);
+    reduce_update_broadcast_kernel<T><<<(uint32_t)blocks, kRowThreads, 0, c->stream>>>(
+        (const T *)stage, world, len, master_of<T>(L->master_w, L->w) + off, L->dv_w + off, L->dm_w + off, dst, lin, hyp);
+    c->launches++;
+    return check_cuda(c, cudaGetLastError(), "reduce + step + broadcast");
+}
+
 template <typename T>
 int apply_update_impl(sk_ctx *c, const sk_dense *L, const float *dw, const float *colsums, uint32_t batch_stat,
                       const sk_optim *lin_, const sk_optim *nrm_, float lr, float clamp, uint32_t step) {
@@ -561,7 +602,7 @@ int sk_sync(sk_ctx *c) {
     if ((rc = check_cuda(c, cudaMemcpy(&flag, c->tc_err, sizeof(int), cudaMemcpyDeviceToHost), "error flag read"))) return rc;
     if (flag != 0) {
         cudaMemset(c->tc_err, 0, sizeof(int));
-        return fail(c, SK_ERR_DEVICE_TIMEOUT, "a tensor-core GEMM gave up waiting on a barrier (role %d: 1 loader, 2 MMA issuer, 3 epilogue)", flag);
+        return fail(c, SK_ERR_DEVICE_TIMEOUT, "a bounded device-side wait gave up (code %d: 1 TMA loader, 2 MMA issuer, 3 GEMM epilogue, 5 peer flags)", flag);
     }
     return SK_OK;
 }
@@ -778,6 +819,124 @@ int sk_apply_vector_update(sk_ctx *c, const sk_dense *L, const float *colsums, u
     if (batch_stat == 0) return fail(c, SK_ERR_INVALID_BATCH_SIZE, "Batch size must be more than zero.");
     if (lin->kind > 1 || nrm->kind > 1) return fail(c, SK_ERR_INVALID_CONFIGURATION, "optimiser ordinal out of range");
     return SK_DISPATCH(L->dtype, apply_vector_update_impl, c, L, colsums, batch_stat, lin, nrm, lr, clamp, step);
+}
+
+static int check_exchange(sk_ctx *c, const sk_dense *L, void *const *ptrs, uint32_t world, uint32_t rank) {
+    if (!ptrs) return fail(c, SK_ERR_NULL_POINTER, "peer pointer table is NULL");
+    if (world == 0 || world > (uint32_t)sk::kMaxRanks || rank >= world)
+        return fail(c, SK_ERR_INVALID_CONFIGURATION, "rank %u of %u ranks (at most %d)", rank, world, sk::kMaxRanks);
+    if (L->dtype == SK_F32) return fail(c, SK_ERR_INVALID_CONFIGURATION, "the fused exchange carries 16-bit gradients only");
+    if (L->K % world != 0 || ((size_t)(L->K / world) * L->N) % 8 != 0)
+        return fail(c, SK_ERR_MISMATCHED_DIMENSIONS, "%u weight rows do not split over %u ranks in whole 16-byte runs", L->K, world);
+    for (uint32_t r = 0; r < world; ++r)
+        if (!ptrs[r] || reinterpret_cast<uintptr_t>(ptrs[r]) % 16 != 0) return fail(c, SK_ERR_NULL_POINTER, "peer pointer %u is NULL or unaligned", r);
+    return SK_OK;
+}
+
+int sk_backward_grads_scatter(sk_ctx *c, const sk_dense *L, const void *x, uint32_t x_rows, uint32_t batch,
+                              uint32_t batch_stat, void *const *peer_stage, uint32_t world, uint32_t rank, float *colsums) {
+    int rc = check_layer(c, L, true);
+    if (rc) return rc;
+    if (!x || !colsums) return fail(c, SK_ERR_NULL_POINTER, "input or output pointer is NULL");
+    if ((rc = check_batch(c, L, x_rows, batch))) return rc;
+    if (batch_stat == 0) return fail(c, SK_ERR_INVALID_BATCH_SIZE, "Batch size must be more than zero.");
+    if ((rc = check_exchange(c, L, peer_stage, world, rank))) return rc;
+    return SK_DISPATCH(L->dtype, backward_grads_scatter_impl, c, L, x, batch, batch_stat, peer_stage, world, rank, colsums);
+}
+
+int sk_reduce_update_broadcast(sk_ctx *c, const sk_dense *L, const void *stage, uint32_t world, uint32_t rank,
+                               void *const *peer_w, const sk_optim *lin, float lr, float clamp, uint32_t step) {
+    int rc = check_layer(c, L, true);
+    if (rc) return rc;
+    if (!stage || !lin) return fail(c, SK_ERR_NULL_POINTER, "staging buffer or optimiser pointer is NULL");
+    if (lin->kind > 1) return fail(c, SK_ERR_INVALID_CONFIGURATION, "optimiser ordinal out of range");
+    if ((rc = check_exchange(c, L, peer_w, world, rank))) return rc;
+    return SK_DISPATCH(L->dtype, reduce_update_broadcast_impl, c, L, stage, world, rank, peer_w, lin, lr, clamp, step);
+}
+
+int sk_peer_alloc(sk_ctx *c, size_t bytes, void **ptr, unsigned char handle_out[64]) {
+    if (!c || !ptr || !handle_out) return SK_ERR_NULL_POINTER;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    if (cudaSetDevice(c->device) != cudaSuccess) return fail(c, SK_ERR_DRIVER, "cannot select device %d", c->device);
+    void *p = nullptr;
+    int rc = check_cuda(c, cudaMalloc(&p, bytes), "exchange arena allocation");
+    if (rc) return rc;
+    if ((rc = check_cuda(c, cudaMemset(p, 0, bytes), "exchange arena clear"))) { cudaFree(p); return rc; }
+    cudaIpcMemHandle_t h;
+    if ((rc = check_cuda(c, cudaIpcGetMemHandle(&h, p), "export exchange arena"))) { cudaFree(p); return rc; }
+    memcpy(handle_out, &h, 64);
+    *ptr = p;
+    return SK_OK;
+}
+
+int sk_peer_open(sk_ctx *c, const unsigned char handle[64], void **ptr) {
+    if (!c || !ptr || !handle) return SK_ERR_NULL_POINTER;
+    if (cudaSetDevice(c->device) != cudaSuccess) return fail(c, SK_ERR_DRIVER, "cannot select device %d", c->device);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    void *p = nullptr;
+    int rc = check_cuda(c, cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess), "map a peer's exchange arena");
+    if (rc) return rc;
+    // host-side sanity: the mapping must be device memory that kernels of this device may dereference
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess || attr.type != cudaMemoryTypeDevice) {
+        cudaGetLastError();
+        cudaIpcCloseMemHandle(p);
+        return fail(c, SK_ERR_DRIVER, "peer mapping is not device memory");
+    }
+    if (attr.device != c->device) {
+        int can = 0;
+        if (cudaDeviceCanAccessPeer(&can, c->device, attr.device) != cudaSuccess || !can) {
+            cudaGetLastError();
+            cudaIpcCloseMemHandle(p);
+            return fail(c, SK_ERR_DRIVER, "device %d cannot access memory of device %d", c->device, attr.device);
+        }
+        cudaError_t e = cudaDeviceEnablePeerAccess(attr.device, 0);
+        if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) { cudaIpcCloseMemHandle(p); return check_cuda(c, e, "enable peer access"); }
+        cudaGetLastError();
+    }
+    *ptr = p;
+    return SK_OK;
+}
+
+int sk_peer_close(sk_ctx *c, void *ptr) {
+    if (!c || !ptr) return SK_ERR_NULL_POINTER;
+    cudaSetDevice(c->device);
+    return check_cuda(c, cudaIpcCloseMemHandle(ptr), "unmap a peer's exchange arena");
+}
+
+int sk_peer_free(sk_ctx *c, void *ptr) {
+    if (!c || !ptr) return SK_ERR_NULL_POINTER;
+    cudaSetDevice(c->device);
+    cudaStreamSynchronize(c->stream);
+    return check_cuda(c, cudaFree(ptr), "free exchange arena");
+}
+
+int sk_copy(sk_ctx *c, void *dst, const void *src, size_t bytes) {
+    if (!c || !dst || !src) return SK_ERR_NULL_POINTER;
+    return check_cuda(c, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, c->stream), "device copy");
+}
+
+int sk_signal_peers(sk_ctx *c, void *const *peer_flags, uint32_t world, uint32_t slot, uint32_t value) {
+    if (!c || !peer_flags) return SK_ERR_NULL_POINTER;
+    if (world == 0 || world > (uint32_t)sk::kMaxRanks) return fail(c, SK_ERR_INVALID_CONFIGURATION, "at most %d ranks", sk::kMaxRanks);
+    sk::PeerPtrs f{};
+    for (uint32_t r = 0; r < world; ++r) {
+        if (!peer_flags[r]) return fail(c, SK_ERR_NULL_POINTER, "flag pointer %u is NULL", r);
+        f.p[r] = peer_flags[r];
+    }
+    sk::signal_peers_kernel<<<1, 32, 0, c->stream>>>(f, world, slot, value);
+    c->launches++;
+    return check_cuda(c, cudaGetLastError(), "signal peers");
+}
+
+int sk_wait_flags(sk_ctx *c, const uint32_t *flags, uint32_t world, uint32_t value) {
+    if (!c || !flags) return SK_ERR_NULL_POINTER;
+    if (world == 0 || world > (uint32_t)sk::kMaxRanks || !c->tc_err) return fail(c, SK_ERR_INVALID_CONFIGURATION, "at most %d ranks", sk::kMaxRanks);
+    sk::wait_flags_kernel<<<1, 32, 0, c->stream>>>(flags, world, value, c->tc_err);
+    c->launches++;
+    c->tc_launches++;   // makes sk_sync read the error word
+    return check_cuda(c, cudaGetLastError(), "wait for peers");
 }
 
 int sk_cast(sk_ctx *c, const void *src, uint32_t sd, void *dst, uint32_t dd, size_t len) {

@@ -421,6 +421,65 @@ weight_update_range_kernel(const G *__restrict__ grad, float grad_scale, T *w, f
     }
 }
 
+// ---- peer exchange (one process per GPU, buffers mapped into each other's address space) ----
+struct PeerPtrs { void *p[kMaxRanks]; };
+
+// Publish `value` in slot `slot` of every rank's flag array (release at system scope, so that
+// everything this GPU wrote before, including peer stores of earlier kernels, is visible first).
+__global__ void signal_peers_kernel(PeerPtrs flags, uint32_t world, uint32_t slot, uint32_t value) {
+    if (threadIdx.x < world) {
+        __threadfence_system();
+        volatile uint32_t *f = reinterpret_cast<volatile uint32_t *>(flags.p[threadIdx.x]) + slot;
+        *f = value;
+        __threadfence_system();
+    }
+}
+
+// Wait until every slot of the local flag array has reached `value`. The wait is bounded (about two
+// seconds of SM clock); on expiry the error word is set and the kernel returns, so a rank that
+// never signals costs an error status, not a hung GPU.
+__global__ void wait_flags_kernel(const uint32_t *flags, uint32_t world, uint32_t value, int *err) {
+    if (threadIdx.x >= world) return;
+    const volatile uint32_t *f = flags + threadIdx.x;
+    const long long t0 = clock64();
+    while ((int32_t)(*f - value) < 0) {
+        if (clock64() - t0 > 4000000000LL) { atomicCAS(err, 0, 5); break; }
+        __nanosleep(200);
+    }
+    __threadfence_system();
+}
+
+// Owner side of the fused exchange: add the `world` staged partial gradients of the rows this
+// rank owns, run the optimiser step on them (f32 master, moments) and write the new 16-bit weights
+// of those rows into every rank's weight tensor (fused all-gather by peer stores).
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+reduce_update_broadcast_kernel(const T *__restrict__ stage, uint32_t world, size_t shard_len, float *master, float *dv,
+                               float *dm, PeerPtrs w_rows, Optim opt, Hyper hyp) {
+    constexpr int V = 8;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < shard_len / V; i += stride) {
+        float g[V], p[V], v[V], m[V];
+#pragma unroll
+        for (int j = 0; j < V; ++j) g[j] = 0.0f;
+        for (uint32_t s = 0; s < world; ++s) {
+            float t[V];
+            load_run<T, V>(stage + s * shard_len + i * V, true, t);
+#pragma unroll
+            for (int j = 0; j < V; ++j) g[j] += t[j];
+        }
+        load_run<float, V>(master + i * V, true, p);
+        load_run<float, V>(dv + i * V, true, v);
+        load_run<float, V>(dm + i * V, true, m);
+#pragma unroll
+        for (int j = 0; j < V; ++j) p[j] = optimiser_step_fast(p[j], v[j], m[j], g[j] * kLossScaleInv, opt, hyp, true);
+        store_run<float, V>(dv + i * V, true, v);
+        store_run<float, V>(dm + i * V, true, m);
+        store_run<float, V>(master + i * V, true, p);
+        for (uint32_t s = 0; s < world; ++s) store_run<T, V>(reinterpret_cast<T *>(w_rows.p[s]) + i * V, true, p);
+    }
+}
+
 // util.cuh:9-19 casts and math.cuh:69-73 fill, grid-stride.
 template <typename S, typename D>
 __global__ void cast_kernel(const S *__restrict__ src, D *__restrict__ dst, size_t len) {

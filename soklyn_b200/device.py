@@ -189,3 +189,42 @@ class GpuContext:
                                              loss_config.loss_func.value, act.ordinal(), act.coeff, lin, nrm,
                                              train_ctx.batch_size, train_ctx.learn_rate, train_ctx.grad_clamp,
                                              step & 0xFFFFFFFF))
+
+    # -- fused exchange over peer-mapped buffers (no counterpart in the reference) --
+    def gpu_backward_grads_scatter(self, layer, input: Tensor, batch_size: int, batch_stat: int, peer_stage, world: int,
+                                   rank: int, colsums: torch.Tensor):
+        self._check(self.lib.sk_backward_grads_scatter(self.handle, C.byref(layer.desc()), input.ptr(), input.rows(),
+                                                       batch_size, batch_stat, peer_stage, world, rank, colsums.data_ptr()))
+
+    def gpu_reduce_update_broadcast(self, layer, stage_ptr: int, world: int, rank: int, peer_w, train_ctx, step: int):
+        lin = _optim(train_ctx.optimiser)
+        self._check(self.lib.sk_reduce_update_broadcast(self.handle, C.byref(layer.desc()), C.c_void_p(stage_ptr), world, rank,
+                                                        peer_w, C.byref(lin), train_ctx.learn_rate, train_ctx.grad_clamp,
+                                                        step & 0xFFFFFFFF))
+
+    def peer_alloc(self, nbytes: int):
+        """(device pointer, 64-byte IPC handle) of a zeroed exchange arena on this context's device."""
+        ptr, handle = C.c_void_p(), C.create_string_buffer(64)
+        self._check(self.lib.sk_peer_alloc(self.handle, nbytes, C.byref(ptr), handle))
+        return ptr.value, handle.raw
+
+    def peer_open(self, handle: bytes) -> int:
+        ptr = C.c_void_p()
+        self._check(self.lib.sk_peer_open(self.handle, handle, C.byref(ptr)))
+        return ptr.value
+
+    def peer_close(self, ptr: int):
+        self._check(self.lib.sk_peer_close(self.handle, C.c_void_p(ptr)))
+
+    def peer_free(self, ptr: int):
+        self._check(self.lib.sk_peer_free(self.handle, C.c_void_p(ptr)))
+
+    def copy_into(self, dst: Tensor, src_ptr: int, nbytes: int):
+        """Device-to-device copy on the context's stream (receive buffer -> weight tensor)."""
+        self._check(self.lib.sk_copy(self.handle, dst.ptr(), C.c_void_p(src_ptr), nbytes))
+
+    def signal_peers(self, peer_flags, world: int, slot: int, value: int):
+        self._check(self.lib.sk_signal_peers(self.handle, peer_flags, world, slot, value & 0xFFFFFFFF))
+
+    def wait_flags(self, flags_ptr: int, world: int, value: int):
+        self._check(self.lib.sk_wait_flags(self.handle, C.c_void_p(flags_ptr), world, value & 0xFFFFFFFF))

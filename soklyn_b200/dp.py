@@ -18,10 +18,20 @@ Two exchange schemes:
   master weights and moments of a rank are then current only for the rows it owns
   (`owned_rows(i)`); the 16-bit weights are complete everywhere.
 
+* "fused" (default for 16-bit blocks on up to 8 GPUs of one node): the same sharding, but without
+  library collectives on the weight path. Every rank maps the other ranks' staging buffers, weight
+  tensors and flag words into its address space (CUDA IPC through torch's tensor sharing). The dW
+  GEMM's epilogue stores each row block straight into the owner's staging buffer over NVLink while the
+  GEMM runs; after a flag handshake the owner adds the staged partials, steps its rows and stores the
+  new 16-bit rows into every rank's weight tensor; a second handshake releases the dX GEMM below.
+  All flag waits are bounded (SK_ERR_DEVICE_TIMEOUT instead of a hang). Only the small column sums
+  still use an NCCL all-reduce.
+
 BatchNorm layers would need their column statistics all-reduced as well; that is not built.
 """
 from __future__ import annotations
 
+import ctypes as C
 from typing import Sequence
 
 import torch
@@ -53,12 +63,13 @@ class DataParallelFFN:
                 raise log.InvalidConfiguration("BatchNorm is not supported under data parallelism")
         dev = context.device
         layers = network.get_layers() if world > 1 else []
+        self.fused = False
         self.sharded = []
         self.dw, self.dw_shard = [], []
         for l in layers:
             k, n = l.get_weights().rows(), l.get_weights().cols()
             can_shard = getattr(l, "precision", None) is not None and l.precision.value != 0 and k % world == 0
-            use = scheme == "sharded" or (scheme == "auto" and can_shard)
+            use = scheme in ("sharded", "fused") or (scheme == "auto" and can_shard)
             if use and not can_shard:
                 raise log.InvalidConfiguration("sharded exchange needs 16-bit blocks whose rows divide by the rank count")
             self.sharded.append(use)
@@ -71,6 +82,57 @@ class DataParallelFFN:
                 self.dw_shard.append(None)
         self.colsums = [torch.empty(3, l.get_weights().cols(), device=dev, dtype=torch.float32) for l in layers]
         self.collectives = 0
+        self.fused = scheme == "fused" or (scheme == "auto" and world > 1 and all(self.sharded) and world <= 8
+                                            and hasattr(context, "signal_peers"))
+        self.epoch = 0
+        if self.fused:
+            self.dw, self.dw_shard = [], []      # the fused exchange stages gradients in its own arena
+            self._map_peers(layers)
+
+    def _map_peers(self, layers):
+        """One exchange arena per rank (staging buffer, receive buffer and flag words of every layer),
+        allocated by the library, exported as a CUDA IPC handle and mapped by every other rank with its
+        own device current. Keeps pointer tables: staging / receive / flags of every rank per layer."""
+        W, es = self.world, layers[0].get_weights().data.element_size()
+        offsets, total = [], 0
+        for l in layers:
+            nbytes = l.get_weights().rows() * l.get_weights().cols() * es
+            pad = lambda v: (v + 255) // 256 * 256
+            off_stage = total
+            off_recv = off_stage + pad(nbytes)
+            off_flags = off_recv + pad(nbytes)
+            total = off_flags + 256
+            offsets.append((off_stage, off_recv, off_flags, nbytes))
+        self._arena, handle = self.ctx.peer_alloc(total)
+        table = [None] * W
+        dist.all_gather_object(table, handle, group=self.group)
+        self._bases = [self._arena if r == self.rank else self.ctx.peer_open(table[r]) for r in range(W)]
+        arr = lambda off: (C.c_void_p * W)(*[b + off for b in self._bases])
+        self.stage_ptr, self.recv_ptr, self.flag_ptr, self.nbytes = [], [], [], []
+        self.p_stage, self.p_recv, self.p_flag_a, self.p_flag_b = [], [], [], []
+        for off_stage, off_recv, off_flags, nbytes in offsets:
+            self.stage_ptr.append(self._arena + off_stage)
+            self.recv_ptr.append(self._arena + off_recv)
+            self.flag_ptr.append(self._arena + off_flags)
+            self.nbytes.append(nbytes)
+            self.p_stage.append(arr(off_stage))
+            self.p_recv.append(arr(off_recv))
+            self.p_flag_a.append(arr(off_flags))
+            self.p_flag_b.append(arr(off_flags + 4 * W))
+        torch.cuda.synchronize(self.ctx.device)
+        dist.barrier(group=self.group)
+
+    def close(self):
+        """Unmap the other ranks' arenas and free this rank's (collective: every rank calls it)."""
+        if getattr(self, "_bases", None):
+            torch.cuda.synchronize(self.ctx.device)
+            dist.barrier(group=self.group)
+            for r, b in enumerate(self._bases):
+                if r != self.rank:
+                    self.ctx.peer_close(b)
+            dist.barrier(group=self.group)
+            self.ctx.peer_free(self._arena)
+            self._bases = None
 
     def owned_rows(self, i: int):
         """(first row, row count) of layer i's weight matrix whose master weights and moments this rank keeps current."""
@@ -100,6 +162,7 @@ class DataParallelFFN:
             self.net.backward(self.ctx, outputs, target, input, loss_config, train_ctx, step)
             return
         last = n - 1
+        self.epoch += 1
         layers[last].compute_loss(self.ctx, target, loss_config)
         for i in range(last, -1, -1):
             layer = layers[i]
@@ -111,6 +174,20 @@ class DataParallelFFN:
                 self.ctx.gpu_backward_pass(layer, x, tc1, step)
                 continue
             tci = train_ctx.get_train_context(i)
+            if self.fused:
+                W, e = self.world, self.epoch
+                self.ctx.gpu_backward_grads_scatter(layer, x, self.local_batch, self.global_batch, self.p_stage[i], W,
+                                                    self.rank, self.colsums[i])
+                self.ctx.signal_peers(self.p_flag_a[i], W, self.rank, e)       # my partials are in place everywhere
+                dist.all_reduce(self.colsums[i], group=self.group)
+                self.ctx.wait_flags(self.flag_ptr[i], W, e)                     # every rank's partials for my rows
+                self.ctx.gpu_reduce_update_broadcast(layer, self.stage_ptr[i], W, self.rank, self.p_recv[i], tci, step)
+                self.ctx.signal_peers(self.p_flag_b[i], W, self.rank, e)       # my rows are in every receive buffer
+                self.ctx.gpu_apply_vector_update(layer, self.colsums[i], self.global_batch, tci, step)
+                self.ctx.wait_flags(self.flag_ptr[i] + 4 * W, W, e)             # all rows of this layer have arrived
+                self.ctx.copy_into(layer.get_weights(), self.recv_ptr[i], self.nbytes[i])
+                self.collectives += 1
+                continue
             if self.sharded[i]:
                 self.ctx.gpu_backward_grads_lp(layer, x, self.local_batch, self.global_batch, self.dw[i], self.colsums[i])
                 dist.reduce_scatter_tensor(self.dw_shard[i], self.dw[i], group=self.group)

@@ -29,17 +29,18 @@ def main():
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     ctx = sk.GpuContext(16, local)
     steps = 3
-    specs = [configs.scaled(configs.CONFIGS[4], dims=(256, 512, 256, 512, 256), batch=256, name="dp_sharded_f16"),
-             configs.scaled(configs.CONFIGS[3], dims=(384, 256, 128, 16), batch=128, name="dp_dropout_layernorm_f16"),
-             configs.scaled(configs.CONFIGS[1], dims=(96, 64, 32, 10), batch=64, name="dp_allreduce_f32")]
+    specs = [(configs.scaled(configs.CONFIGS[4], dims=(256, 512, 256, 512, 256), batch=256, name="dp_fused_f16"), "fused"),
+             (configs.scaled(configs.CONFIGS[4], dims=(256, 512, 256, 512, 256), batch=256, name="dp_sharded_f16"), "sharded"),
+             (configs.scaled(configs.CONFIGS[3], dims=(384, 256, 128, 16), batch=128, name="dp_dropout_layernorm_f16"), "auto"),
+             (configs.scaled(configs.CONFIGS[1], dims=(96, 64, 32, 10), batch=64, name="dp_allreduce_f32"), "auto")]
     ok = True
-    for spec in specs:
+    for spec, scheme in specs:
         w = configs.make_weights(spec)
         x, t, _ = configs.make_data(spec)
         per = spec.batch // world
         reset_tensor_ids(0)
         net = configs.build_network(ctx, spec, w, max_batch=per)
-        dp = DataParallelFFN(ctx, net, spec.batch, rank, world)
+        dp = DataParallelFFN(ctx, net, spec.batch, rank, world, scheme=scheme)
         xs = Tensor.from_cpu_vector(ctx, x[rank * per:(rank + 1) * per], (per, spec.dims[0]), spec.prec())
         ts = Tensor.from_cpu_vector(ctx, t[rank * per:(rank + 1) * per], (per, spec.dims[-1]), spec.prec())
         lrs = H.lr_schedule(spec, steps)
@@ -53,6 +54,7 @@ def main():
             ref = wt.clone()
             dist.broadcast(ref, 0)
             assert torch.equal(wt, ref), f"{spec.name}: layer {i} weights differ between ranks"
+        dp.close() if hasattr(dp, "close") else None
         if rank == 0:
             single, _ = H.run_device(ctx, spec, w, x, t, steps)
             tol = 1e-2 if spec.precision != "f32" else 5e-4
@@ -69,7 +71,7 @@ def main():
                 ma, mb = a.get_masks().download(ctx)[:per], b.get_masks().download(ctx)[:per]
                 mask_ok = np.array_equal(ma != 0, mb != 0)
                 print(f"{spec.name} L{i}: weights rel {rel:.2e} (max moved {moved.max():.2f} lr), outputs rel {rel_o:.2e}, "
-                      f"masks {'equal' if mask_ok else 'DIFFER'}, sharded={dp.sharded[i]}", flush=True)
+                      f"masks {'equal' if mask_ok else 'DIFFER'}, sharded={dp.sharded[i]}, fused={dp.fused}", flush=True)
                 ok = ok and good and mask_ok and rel_o <= 5 * tol
     flag = torch.tensor([1 if ok else 0], device=ctx.device)
     dist.broadcast(flag, 0)
