@@ -305,8 +305,21 @@ int hidden_error_impl(sk_ctx *c, const sk_dense *cur, const sk_dense *next, uint
     const T *dy = f32 ? (const T *)next->d_prenorm : (const T *)next->d_prenorm_lp;
     const T *wn = f32 ? (const T *)master_of<T>(next->master_w, next->w) : (const T *)next->w;
     ProfScope ps(c, SK_PROF_GEMM_DX);
-    int rc = check_cuda(c, run_gemm<T, T, true, false>(c, cur->dtype, dy, ec, wn, ec, batch, cur->N, ec, epi),
-                        "hidden error gemm");
+    cudaError_t e;
+    // kernels specialised for the activation / normalisation pairs of the wide and the classifier networks
+    if (!f32 && cur->act == SK_ACT_SILU && cur->norm == SK_NORM_RMS) {
+        EpiHidden<T, SK_ACT_SILU, SK_NORM_RMS> se;
+        static_assert(sizeof(se) == sizeof(epi), "specialised functor has the same fields");
+        memcpy(&se, &epi, sizeof se);
+        e = run_gemm<T, T, true, false>(c, cur->dtype, dy, ec, wn, ec, batch, cur->N, ec, se);
+    } else if (!f32 && cur->act == SK_ACT_MISH && cur->norm == SK_NORM_LAYER) {
+        EpiHidden<T, SK_ACT_MISH, SK_NORM_LAYER> se;
+        memcpy(&se, &epi, sizeof se);
+        e = run_gemm<T, T, true, false>(c, cur->dtype, dy, ec, wn, ec, batch, cur->N, ec, se);
+    } else {
+        e = run_gemm<T, T, true, false>(c, cur->dtype, dy, ec, wn, ec, batch, cur->N, ec, epi);
+    }
+    int rc = check_cuda(c, e, "hidden error gemm");
     c->launches++;
     return rc;
 }
@@ -361,13 +374,20 @@ int backward_update_impl(sk_ctx *c, const sk_dense *L, const void *x, uint32_t b
     epi.N = L->N; epi.opt = lin; epi.hyp = hyp;
     epi.vec_ok = L->N % 8 == 0 && aligned16(L->w) && aligned16(epi.master) && aligned16(L->dv_w) && aligned16(L->dm_w);
     ProfScope ps(c, SK_PROF_GEMM_DW);
-    if (f32)
+    if (f32) {
         rc = check_cuda(c, run_gemm<T, float, false, true>(c, L->dtype, (const T *)x, L->K, L->d_prenorm,
                                                                     L->N, L->K, L->N, batch, epi), "weight gradient gemm");
-    else
+    } else if (lin.kind == SK_OPT_ADAM && L->regu == SK_REGU_NONE) {   // specialised: Adam, no regularisation
+        EpiWeightUpdate<T, SK_OPT_ADAM, SK_REGU_NONE> se;
+        static_assert(sizeof(se) == sizeof(epi), "specialised functor has the same fields");
+        memcpy(&se, &epi, sizeof se);
+        rc = check_cuda(c, run_gemm<T, T, false, true>(c, L->dtype, (const T *)x, L->K, (const T *)L->d_prenorm_lp, L->N,
+                                                        L->K, L->N, batch, se), "weight gradient gemm");
+    } else {
         rc = check_cuda(c, run_gemm<T, T, false, true>(c, L->dtype, (const T *)x, L->K,
                                                                 (const T *)L->d_prenorm_lp, L->N, L->K, L->N, batch, epi),
                         "weight gradient gemm");
+    }
     c->launches++;
     return rc;
 }

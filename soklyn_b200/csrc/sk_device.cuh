@@ -252,16 +252,21 @@ __device__ __forceinline__ float sqrt_approx(float x) {
 
 // The same step with the two bias corrections as multiplications by host-side reciprocals and
 // the final quotient through rcp/sqrt approximations (relative error ~1e-7 on the update).
+// KIND / REGU >= 0 fix the optimiser and the regularisation at compile time (the kernels that
+// are specialised for the common cases), -1 reads them from the arguments.
+template <int KIND = -1, int REGU = -1>
 __device__ __forceinline__ float optimiser_step_fast(float p, float &v, float &mo, float acc, const Optim &o,
                                                      const Hyper &h, bool apply_regu) {
     const float g = acc * h.inv_m;
-    if (apply_regu && h.regu) {
+    const uint32_t regu = REGU >= 0 ? (uint32_t)REGU : h.regu;
+    const uint32_t kind = KIND >= 0 ? (uint32_t)KIND : o.kind;
+    if (apply_regu && regu) {
         const float sign = p > 0.0f ? 1.0f : (p < 0.0f ? -1.0f : 0.0f);
-        if (h.regu == 1) p -= h.regu_coeff * sign;
-        if (h.regu == 2) p -= 2.0f * h.regu_coeff * p;
+        if (regu == 1) p -= h.regu_coeff * sign;
+        if (regu == 2) p -= 2.0f * h.regu_coeff * p;
     }
     float u;
-    if (o.kind == 0) {
+    if (kind == 0) {
         v = o.beta1 * v + g;
         u = h.lr * (o.nesterov ? g + o.beta1 * v : v);
     } else {

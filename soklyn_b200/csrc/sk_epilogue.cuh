@@ -152,7 +152,9 @@ template <typename T> struct EpiForward {
 
 // ---- hidden delta: S = dY_next . W_next^T, times act', times mask, normalisation backward ----
 // Reference: ffn/backward.cu:59-102 and util.cu:175-215 (loss scale 1).
-template <typename T> struct EpiHidden {
+// ACT / NORM >= 0 fix the activation and the normalisation at compile time (specialised kernels
+// for the common pairs, with every mode switch folded away); -1 reads them from the fields.
+template <typename T, int ACT = -1, int NORM = -1> struct EpiHidden {
     const T *predrop, *preact, *mask, *prenorm, *centered, *rstd;
     const float *norm_w;   // f32 master copy of the normalisation weights
     float *grad, *d_prenorm, *d_norm_w, *d_norm_b;
@@ -160,6 +162,9 @@ template <typename T> struct EpiHidden {
     uint32_t N, norm, act;
     float leaky, inv_n, inv_m;
     bool vec_ok;
+
+    __device__ __forceinline__ uint32_t A() const { return ACT >= 0 ? (uint32_t)ACT : act; }
+    __device__ __forceinline__ uint32_t Nm() const { return NORM >= 0 ? (uint32_t)NORM : norm; }
 
     __device__ __forceinline__ void one(uint32_t row, uint32_t col, float s) const {
         const size_t idx = (size_t)row * N + col;
@@ -186,13 +191,13 @@ template <typename T> struct EpiHidden {
         float gr[V], dp[V], gw[V], gb[V];
 #pragma unroll
         for (int j = 0; j < V; ++j) gr[j] = acc[j];
-        activation_derivative_v<kFastMath<T>, V>(act, gr, pd, pa, leaky);
+        activation_derivative_v<kFastMath<T>, V>(A(), gr, pd, pa, leaky);
 #pragma unroll
         for (int j = 0; j < V; ++j) gr[j] *= mk[j];
-        if (norm == 0) {
+        if (Nm() == 0) {
 #pragma unroll
             for (int j = 0; j < V; ++j) { dp[j] = gr[j]; gw[j] = 0.0f; gb[j] = 0.0f; }
-        } else if (norm == 1) {
+        } else if (Nm() == 1) {
 #pragma unroll
             for (int j = 0; j < V; ++j) {
                 const float r = rs[j];
@@ -201,7 +206,7 @@ template <typename T> struct EpiHidden {
                 dp[j] = nw[j] * r * (gr[j] - r * r * xv[j] * xv[j] * inv_n);
             }
         } else {
-            const float inv = norm == 2 ? inv_n : inv_m;
+            const float inv = Nm() == 2 ? inv_n : inv_m;
 #pragma unroll
             for (int j = 0; j < V; ++j) {
                 const float r = rs[j];
@@ -228,11 +233,11 @@ template <typename T> struct EpiHidden {
         load_run<T, V>(predrop + idx, true, pd);
         load_run<T, V>(preact + idx, true, pa);
         load_run<T, V>(mask + idx, true, mk);
-        if (norm == 1) load_run<T, V>(prenorm + idx, true, xv);
-        else if (norm >= 2) load_run<T, V>(centered + idx, true, xv);
-        if (norm) load_run<float, V>(norm_w + col0, true, nw);
-        if (norm == 3) load_run<T, V>(rstd + col0, true, rs);
-        else if (norm) {
+        if (Nm() == 1) load_run<T, V>(prenorm + idx, true, xv);
+        else if (Nm() >= 2) load_run<T, V>(centered + idx, true, xv);
+        if (Nm()) load_run<float, V>(norm_w + col0, true, nw);
+        if (Nm() == 3) load_run<T, V>(rstd + col0, true, rs);
+        else if (Nm()) {
             const float r = to_f32(rstd[row]);
 #pragma unroll
             for (int j = 0; j < V; ++j) rs[j] = r;
@@ -243,28 +248,28 @@ template <typename T> struct EpiHidden {
     struct Cols { float nw[8], rs[8]; };
     struct Pre { Pack<T, 8> pd, pa, mk, xv; T rrow; };
     __device__ __forceinline__ void cols(uint32_t col0, Cols &c) const {
-        if (norm) load_run<float, 8>(norm_w + col0, true, c.nw);
-        if (norm == 3) load_run<T, 8>(rstd + col0, true, c.rs);
+        if (Nm()) load_run<float, 8>(norm_w + col0, true, c.nw);
+        if (Nm() == 3) load_run<T, 8>(rstd + col0, true, c.rs);
     }
     __device__ __forceinline__ void prefetch(uint32_t row, uint32_t col0, Pre &p) const {
         const size_t idx = (size_t)row * N + col0;
         p.pd = load_pack<T, 8>(predrop + idx);
         p.pa = load_pack<T, 8>(preact + idx);
         p.mk = load_pack<T, 8>(mask + idx);
-        if (norm == 1) p.xv = load_pack<T, 8>(prenorm + idx);
-        else if (norm >= 2) p.xv = load_pack<T, 8>(centered + idx);
-        if (norm == 1 || norm == 2) p.rrow = rstd[row];
+        if (Nm() == 1) p.xv = load_pack<T, 8>(prenorm + idx);
+        else if (Nm() >= 2) p.xv = load_pack<T, 8>(centered + idx);
+        if (Nm() == 1 || Nm() == 2) p.rrow = rstd[row];
     }
     __device__ __forceinline__ void finish(uint32_t row, uint32_t col0, const float (&acc)[8], const Pre &p, const Cols &c) const {
         float pd[8], pa[8], mk[8], xv[8], rs[8];
         unpack<T, 8>(p.pd, pd);
         unpack<T, 8>(p.pa, pa);
         unpack<T, 8>(p.mk, mk);
-        if (norm) unpack<T, 8>(p.xv, xv);
-        if (norm == 3) {
+        if (Nm()) unpack<T, 8>(p.xv, xv);
+        if (Nm() == 3) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) rs[j] = c.rs[j];
-        } else if (norm) {
+        } else if (Nm()) {
             const float r = to_f32(p.rrow);
 #pragma unroll
             for (int j = 0; j < 8; ++j) rs[j] = r;
@@ -275,7 +280,7 @@ template <typename T> struct EpiHidden {
 
 // ---- weight gradient with the optimiser step fused in ------------------------------------------
 // Reference: ffn/backward.cu:157-234 (dW part) with :105-154.
-template <typename T> struct EpiWeightUpdate {
+template <typename T, int KIND = -1, int REGU = -1> struct EpiWeightUpdate {
     T *w;
     float *master, *dv, *dm;   // master == (float*)w in f32 mode
     uint32_t N;
@@ -333,7 +338,7 @@ template <typename T> struct EpiWeightUpdate {
         unpack<float, 8>(q.v, v);
         unpack<float, 8>(q.m, m);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) p[j] = optimiser_step_fast(p[j], v[j], m[j], acc[j] * kLossScaleInv, opt, hyp, true);
+        for (int j = 0; j < 8; ++j) p[j] = optimiser_step_fast<KIND, REGU>(p[j], v[j], m[j], acc[j] * kLossScaleInv, opt, hyp, true);
         store_run<float, 8>(dv + idx, true, v);
         store_run<float, 8>(dm + idx, true, m);
         store_run<float, 8>(master + idx, true, p);
