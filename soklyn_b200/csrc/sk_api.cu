@@ -4,6 +4,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <type_traits>
@@ -125,7 +126,9 @@ cudaError_t launch_tc_bn(sk_ctx *c, const CUtensorMap *ta, const CUtensorMap *tb
     const uint32_t tiles = ((M + kTcBM - 1) / kTcBM) * ((N + BN - 1) / BN);
     const uint32_t grid = tiles < (uint32_t)c->num_sms ? tiles : (uint32_t)c->num_sms;
     const uint32_t idesc = tc::make_instr_desc(std::is_same<T, __nv_bfloat16>::value ? 1u : 0u, A_MN, B_MN, kTcBM, BN);
-    kernel<<<grid, kTcThreads, S::kSmemBytes, c->stream>>>(*ta, *tb, M, N, K, idesc, epi, c->tc_err);
+    uint32_t group_n = 8;
+    if (const char *env = getenv("SK_TC_GROUP_N")) { const int v = atoi(env); if (v >= 1 && v <= 64) group_n = (uint32_t)v; }
+    kernel<<<grid, kTcThreads, S::kSmemBytes, c->stream>>>(*ta, *tb, M, N, K, idesc, group_n, epi, c->tc_err);
     c->tc_launches++;
     return cudaGetLastError();
 }

@@ -42,22 +42,22 @@ template <int BN> struct TcShape {
 
 enum : int { kTcErrProducer = 1, kTcErrMma = 2, kTcErrEpilogue = 3 };
 
-// Tile order. Tiles are walked in groups of kTcGroupN tile-columns, row-major inside a group, so
+// Tile order. Tiles are walked in groups of group_n tile-columns (8 by default), row-major inside a group, so
 // that the ~148 tiles in flight form a compact block (about 18 x 8 tiles): the B panels of a group
 // stay in L2 while A streams past once per group, instead of once per tile-column.
-constexpr uint32_t kTcGroupN = 8;
-__device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uint32_t tiles_n, uint32_t &mi, uint32_t &ni) {
-    const uint32_t group_tiles = kTcGroupN * tiles_m;
+__device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uint32_t tiles_n, uint32_t group_n,
+                                            uint32_t &mi, uint32_t &ni) {
+    const uint32_t group_tiles = group_n * tiles_m;
     const uint32_t g = tile / group_tiles, r = tile - g * group_tiles;
-    const uint32_t width = min(kTcGroupN, tiles_n - g * kTcGroupN);
+    const uint32_t width = min(group_n, tiles_n - g * group_n);
     mi = r / width;
-    ni = g * kTcGroupN + (r - mi * width);
+    ni = g * group_n + (r - mi * width);
 }
 
 template <bool A_MN, bool B_MN, int BN, class Epi>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               uint32_t M, uint32_t N, uint32_t K, uint32_t idesc, Epi epi, int *err_flag) {
+               uint32_t M, uint32_t N, uint32_t K, uint32_t idesc, uint32_t group_n, Epi epi, int *err_flag) {
     using S = TcShape<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -97,7 +97,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             bool ok = true;
             for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 uint32_t mi, ni;
-                tile_coords(tile, tiles_m, tiles_n, mi, ni);
+                tile_coords(tile, tiles_m, tiles_n, group_n, mi, ni);
                 const int32_t m0 = mi * kTcBM, n0 = ni * BN;
                 for (uint32_t kb = 0; kb < num_kb; ++kb) {
                     if (!tc::mbar_wait(&empty_bar[stage], phase ^ 1)) { ok = false; break; }
@@ -161,7 +161,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         bool ok = true;
         for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
             uint32_t mi, ni;
-            tile_coords(tile, tiles_m, tiles_n, mi, ni);
+            tile_coords(tile, tiles_m, tiles_n, group_n, mi, ni);
             const uint32_t m0 = mi * kTcBM, n0 = ni * BN;
             if (!tc::mbar_wait(&tmem_full[acc], acc_phase)) { ok = false; break; }
             tc::tc_fence_after_sync();

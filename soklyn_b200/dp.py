@@ -44,6 +44,23 @@ from .ffn import FeedForwardNetwork
 from .function import Normalisation
 
 
+class _ArenaView:
+    """Exposes a range of an exchange arena through __cuda_array_interface__ (as 16-bit integers)."""
+
+    def __init__(self, ptr: int, count: int):
+        self.__cuda_array_interface__ = {"shape": (count,), "typestr": "<i2", "data": (ptr, False), "version": 2}
+
+
+def _alias_tensor(ptr: int, shape, dtype, device) -> torch.Tensor:
+    """A torch tensor of a 16-bit dtype over library-owned device memory (no copy, no ownership)."""
+    count = 1
+    for d in shape:
+        count *= d
+    raw = torch.as_tensor(_ArenaView(ptr, count), device=device)
+    assert raw.data_ptr() == ptr, "torch copied the arena range instead of aliasing it"
+    return raw.view(dtype).view(*shape)
+
+
 def shard_rows(global_batch: int, rank: int, world: int):
     """(first row, row count) of this rank's contiguous shard; the batch must divide evenly."""
     if global_batch % world != 0:
@@ -119,6 +136,16 @@ class DataParallelFFN:
             self.p_recv.append(arr(off_recv))
             self.p_flag_a.append(arr(off_flags))
             self.p_flag_b.append(arr(off_flags + 4 * W))
+        # The receive buffer of a layer becomes the storage of its weight tensor: the owners' stores land
+        # directly in every rank's weights and no copy is needed after the second handshake.
+        self._own_w = []
+        for l, rp in zip(layers, self.recv_ptr):
+            w = l.get_weights()
+            self._own_w.append(w.data)
+            alias = _alias_tensor(rp, tuple(w.data.shape), w.data.dtype, self.ctx.device)
+            alias.copy_(w.data)
+            w.data = alias
+            l._desc = None
         torch.cuda.synchronize(self.ctx.device)
         dist.barrier(group=self.group)
 
@@ -127,6 +154,11 @@ class DataParallelFFN:
         if getattr(self, "_bases", None):
             torch.cuda.synchronize(self.ctx.device)
             dist.barrier(group=self.group)
+            for l, own in zip(self.net.get_layers(), self._own_w):   # weights move back to their own storage
+                own.copy_(l.get_weights().data)
+                l.get_weights().data = own
+                l._desc = None
+            torch.cuda.synchronize(self.ctx.device)
             for r, b in enumerate(self._bases):
                 if r != self.rank:
                     self.ctx.peer_close(b)
@@ -185,7 +217,6 @@ class DataParallelFFN:
                 self.ctx.signal_peers(self.p_flag_b[i], W, self.rank, e)       # my rows are in every receive buffer
                 self.ctx.gpu_apply_vector_update(layer, self.colsums[i], self.global_batch, tci, step)
                 self.ctx.wait_flags(self.flag_ptr[i] + 4 * W, W, e)             # all rows of this layer have arrived
-                self.ctx.copy_into(layer.get_weights(), self.recv_ptr[i], self.nbytes[i])
                 self.collectives += 1
                 continue
             if self.sharded[i]:
