@@ -188,22 +188,18 @@ int sk_apply_vector_update(sk_ctx *ctx, const sk_dense *layer, const float *cols
                            uint32_t step);
 
 /* Fused form of the exchange for one process per GPU with peer-mapped buffers (no counterpart).
- * Rank r owns rows [r*K/W, (r+1)*K/W) of each weight matrix and keeps a staging buffer
- * T [W][K/W][N]. sk_backward_grads_scatter runs the dW GEMM and its epilogue stores every row block,
- * averaged and in the storage type, into slot `rank` of the owner's staging buffer over NVLink
- * (peer_stage[i] = staging buffer of rank i as mapped here). sk_signal_peers publishes a value in
- * slot `slot` of every rank's flag array; sk_wait_flags waits (bounded: about two seconds, then
- * SK_ERR_DEVICE_TIMEOUT at the next sk_sync) until all `world` slots of the local array reached it.
- * sk_reduce_update_broadcast adds the W staged partials of the owned rows, steps them and writes the
- * new 16-bit rows into row range `rank` of every rank's receive buffer T [K][N] (peer_w[i] = receive
- * buffer of rank i), from where each rank copies them into its weight tensor after the second
- * handshake. Staging, receive buffers and flag words live in the ranks' exchange arenas. */
-int sk_backward_grads_scatter(sk_ctx *ctx, const sk_dense *layer, const void *x, uint32_t x_rows, uint32_t batch,
-                              uint32_t batch_stat, void *const *peer_stage, uint32_t world, uint32_t rank,
-                              float *colsums);
-int sk_reduce_update_broadcast(sk_ctx *ctx, const sk_dense *layer, const void *stage, uint32_t world, uint32_t rank,
-                               void *const *peer_w, const sk_optim *linear, float learn_rate, float grad_clamp,
-                               uint32_t step);
+ * Rank r owns rows [r*K/W, (r+1)*K/W) of each weight matrix. Every rank writes its averaged 16-bit dW
+ * (sk_backward_grads_lp) into a gradient buffer T [K][N] inside its exchange arena; sk_signal_peers
+ * publishes a value in slot `slot` of every rank's flag array and sk_wait_flags waits (bounded: about two
+ * seconds, then SK_ERR_DEVICE_TIMEOUT at the next sk_sync) until all `world` slots of the local array
+ * reached it. sk_reduce_update_broadcast is then reduce-scatter + optimiser + all-gather in ONE kernel:
+ * it pulls the owned rows out of every rank's gradient buffer over NVLink (peer_grad[i] = gradient
+ * buffer of rank i as mapped here), adds them, steps them (f32 master, moments) and stores the new
+ * 16-bit rows into every rank's weight tensor (peer_w[i] = weight tensor of rank i, which therefore
+ * lives in that rank's arena too). A second handshake releases the dX GEMM of the layer below. */
+int sk_reduce_update_broadcast(sk_ctx *ctx, const sk_dense *layer, void *const *peer_grad, uint32_t world,
+                               uint32_t rank, void *const *peer_w, const sk_optim *linear, float learn_rate,
+                               float grad_clamp, uint32_t step);
 /* Exchange arena of one rank: sk_peer_alloc allocates `bytes` of zeroed device memory (set-up time,
  * not the hot path) and returns a 64-byte CUDA IPC handle for it; the other ranks (other processes
  * on the same node) turn that handle into a pointer usable by kernels of THEIR device with

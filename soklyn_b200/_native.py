@@ -123,8 +123,6 @@ _SIGS = {
                                        C.POINTER(SkOptim), C.c_float, C.c_float, C.c_uint32]),
     "sk_apply_vector_update": (C.c_int, [C.c_void_p, C.POINTER(SkDense), C.c_void_p, C.c_uint32, C.POINTER(SkOptim),
                                          C.POINTER(SkOptim), C.c_float, C.c_float, C.c_uint32]),
-    "sk_backward_grads_scatter": (C.c_int, [C.c_void_p, C.POINTER(SkDense), C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32,
-                                            C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p]),
     "sk_reduce_update_broadcast": (C.c_int, [C.c_void_p, C.POINTER(SkDense), C.c_void_p, C.c_uint32, C.c_uint32,
                                              C.c_void_p, C.POINTER(SkOptim), C.c_float, C.c_float, C.c_uint32]),
     "sk_copy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),

@@ -471,43 +471,22 @@ int apply_vector_update_impl(sk_ctx *c, const sk_dense *L, const float *colsums,
     return vector_update_launch<T>(c, L, colsums, 1, lin, nrm, hyp);
 }
 
-// dW GEMM whose epilogue scatters each row block to the staging buffer of the rank that owns it.
 template <typename T>
-int backward_grads_scatter_impl(sk_ctx *c, const sk_dense *L, const void *x, uint32_t batch, uint32_t batch_stat,
-                                void *const *peer_stage, uint32_t world, uint32_t rank, float *colsums) {
-    int rc = SK_OK;
-    const uint32_t nblocks = launch_colsum_partial(c, L, batch, &rc);
-    if (rc) return rc;
-    colsum_final_kernel<<<(3 * L->N + 255) / 256, 256, 0, c->stream>>>((const float *)c->workspace, colsums, L->N, nblocks);
-    c->launches++;
-    if ((rc = check_cuda(c, cudaGetLastError(), "column sums (final)"))) return rc;
-    EpiPeerScatter<T> epi{};
-    bool vec = L->N % 8 == 0;
-    for (uint32_t r = 0; r < world; ++r) { epi.stage[r] = (T *)peer_stage[r]; vec = vec && aligned16(peer_stage[r]); }
-    epi.rows_per_rank = L->K / world; epi.my_rank = rank; epi.N = L->N; epi.scale = 1.0f / (float)batch_stat; epi.vec_ok = vec;
-    ProfScope ps(c, SK_PROF_GEMM_DW);
-    rc = check_cuda(c, run_gemm<T, T, false, true>(c, L->dtype, (const T *)x, L->K, (const T *)L->d_prenorm_lp, L->N, L->K,
-                                                    L->N, batch, epi), "weight gradient gemm (scatter)");
-    c->launches++;
-    return rc;
-}
-
-template <typename T>
-int reduce_update_broadcast_impl(sk_ctx *c, const sk_dense *L, const void *stage, uint32_t world, uint32_t rank,
+int reduce_update_broadcast_impl(sk_ctx *c, const sk_dense *L, void *const *peer_grad, uint32_t world, uint32_t rank,
                                  void *const *peer_w, const sk_optim *lin_, float lr, float clamp, uint32_t step) {
     const Optim lin = make_optim(lin_, step);
     const Hyper hyp{lr, clamp, 1.0f, L->regu, L->regu_coeff};   // the staged gradients are already averaged
     const uint32_t rows = L->K / world;
     const size_t off = (size_t)rank * rows * L->N, len = (size_t)rows * L->N;
-    PeerPtrs dst{};
-    for (uint32_t r = 0; r < world; ++r) dst.p[r] = (T *)peer_w[r] + off;
+    PeerPtrs dst{}, src{};
+    for (uint32_t r = 0; r < world; ++r) { dst.p[r] = (T *)peer_w[r] + off; src.p[r] = (T *)peer_grad[r] + off; }
     size_t blocks = (len / 8 + kRowThreads - 1) / kRowThreads;
     const size_t cap = (size_t)c->num_sms * 8;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     ProfScope ps(c, SK_PROF_UPDATE);
     reduce_update_broadcast_kernel<T><<<(uint32_t)blocks, kRowThreads, 0, c->stream>>>(
-        (const T *)stage, world, len, master_of<T>(L->master_w, L->w) + off, L->dv_w + off, L->dm_w + off, dst, lin, hyp);
+        src, world, len, master_of<T>(L->master_w, L->w) + off, L->dv_w + off, L->dm_w + off, dst, lin, hyp);
     c->launches++;
     return check_cuda(c, cudaGetLastError(), "reduce + step + broadcast");
 }
@@ -856,25 +835,15 @@ static int check_exchange(sk_ctx *c, const sk_dense *L, void *const *ptrs, uint3
     return SK_OK;
 }
 
-int sk_backward_grads_scatter(sk_ctx *c, const sk_dense *L, const void *x, uint32_t x_rows, uint32_t batch,
-                              uint32_t batch_stat, void *const *peer_stage, uint32_t world, uint32_t rank, float *colsums) {
-    int rc = check_layer(c, L, true);
-    if (rc) return rc;
-    if (!x || !colsums) return fail(c, SK_ERR_NULL_POINTER, "input or output pointer is NULL");
-    if ((rc = check_batch(c, L, x_rows, batch))) return rc;
-    if (batch_stat == 0) return fail(c, SK_ERR_INVALID_BATCH_SIZE, "Batch size must be more than zero.");
-    if ((rc = check_exchange(c, L, peer_stage, world, rank))) return rc;
-    return SK_DISPATCH(L->dtype, backward_grads_scatter_impl, c, L, x, batch, batch_stat, peer_stage, world, rank, colsums);
-}
-
-int sk_reduce_update_broadcast(sk_ctx *c, const sk_dense *L, const void *stage, uint32_t world, uint32_t rank,
+int sk_reduce_update_broadcast(sk_ctx *c, const sk_dense *L, void *const *peer_grad, uint32_t world, uint32_t rank,
                                void *const *peer_w, const sk_optim *lin, float lr, float clamp, uint32_t step) {
     int rc = check_layer(c, L, true);
     if (rc) return rc;
-    if (!stage || !lin) return fail(c, SK_ERR_NULL_POINTER, "staging buffer or optimiser pointer is NULL");
+    if (!lin) return fail(c, SK_ERR_NULL_POINTER, "optimiser pointer is NULL");
     if (lin->kind > 1) return fail(c, SK_ERR_INVALID_CONFIGURATION, "optimiser ordinal out of range");
+    if ((rc = check_exchange(c, L, peer_grad, world, rank))) return rc;
     if ((rc = check_exchange(c, L, peer_w, world, rank))) return rc;
-    return SK_DISPATCH(L->dtype, reduce_update_broadcast_impl, c, L, stage, world, rank, peer_w, lin, lr, clamp, step);
+    return SK_DISPATCH(L->dtype, reduce_update_broadcast_impl, c, L, peer_grad, world, rank, peer_w, lin, lr, clamp, step);
 }
 
 int sk_peer_alloc(sk_ctx *c, size_t bytes, void **ptr, unsigned char handle_out[64]) {

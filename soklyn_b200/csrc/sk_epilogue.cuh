@@ -392,35 +392,6 @@ template <typename T> struct EpiStoreScaled {
     }
 };
 
-// ---- dW tile pushed straight into the gradient staging buffer of the rank that owns its rows ----
-// Fused GEMM + reduce-scatter over NVLink: row r of dW belongs to rank r / rows_per_rank; every rank
-// keeps a staging buffer [world][rows_per_rank][N] in the storage type and slot `my_rank` of the
-// owner's buffer receives this rank's partial sum (already averaged, loss scale kept) by plain peer
-// stores, tile by tile while the GEMM runs. The owner adds the slots (reduce_update_broadcast_kernel).
-constexpr int kMaxRanks = 8;
-template <typename T> struct EpiPeerScatter {
-    T *stage[kMaxRanks];       // staging buffer of every rank (peer pointers; [my_rank] is local)
-    uint32_t rows_per_rank, my_rank, N;
-    float scale;
-    bool vec_ok;
-    template <int V>
-    __device__ __forceinline__ void run(uint32_t row, uint32_t col0, const float (&acc)[V], uint32_t ncols) const {
-        const uint32_t owner = row / rows_per_rank, local = row - owner * rows_per_rank;
-        T *dst = stage[owner] + ((size_t)my_rank * rows_per_rank + local) * N + col0;
-        float v[V];
-#pragma unroll
-        for (int j = 0; j < V; ++j) v[j] = acc[j] * scale;
-        if (vec_ok && ncols == V) store_run<T, V>(dst, true, v);
-        else for (uint32_t j = 0; j < ncols; ++j) dst[j] = from_f32<T>(v[j]);
-    }
-
-    struct Cols {};
-    using Pre = NoPre;
-    __device__ __forceinline__ void cols(uint32_t, Cols &) const {}
-    __device__ __forceinline__ void prefetch(uint32_t, uint32_t, Pre &) const {}
-    __device__ __forceinline__ void finish(uint32_t row, uint32_t col0, const float (&acc)[8], const Pre &, const Cols &) const {
-        run<8>(row, col0, acc, 8);
-    }
-};
+constexpr int kMaxRanks = 8;   // ranks of one NVSwitch domain the fused exchange addresses
 
 } // namespace sk

@@ -449,12 +449,13 @@ __global__ void wait_flags_kernel(const uint32_t *flags, uint32_t world, uint32_
     __threadfence_system();
 }
 
-// Owner side of the fused exchange: add the `world` staged partial gradients of the rows this
-// rank owns, run the optimiser step on them (f32 master, moments) and write the new 16-bit weights
-// of those rows into every rank's weight tensor (fused all-gather by peer stores).
+// Owner side of the fused exchange, reduce-scatter + optimiser + all-gather in one kernel: pull the
+// rows this rank owns out of every rank's gradient buffer (peer loads over NVLink, 512 contiguous
+// bytes per warp), add them, run the optimiser step (f32 master, moments) and store the new 16-bit
+// rows into every rank's weight tensor (peer stores). Loads and stores use opposite NVLink directions.
 template <typename T>
 __global__ void __launch_bounds__(kRowThreads)
-reduce_update_broadcast_kernel(const T *__restrict__ stage, uint32_t world, size_t shard_len, float *master, float *dv,
+reduce_update_broadcast_kernel(PeerPtrs grad_rows, uint32_t world, size_t shard_len, float *master, float *dv,
                                float *dm, PeerPtrs w_rows, Optim opt, Hyper hyp) {
     constexpr int V = 8;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -462,12 +463,16 @@ reduce_update_broadcast_kernel(const T *__restrict__ stage, uint32_t world, size
         float g[V], p[V], v[V], m[V];
 #pragma unroll
         for (int j = 0; j < V; ++j) g[j] = 0.0f;
-        for (uint32_t s = 0; s < world; ++s) {
-            float t[V];
-            load_run<T, V>(stage + s * shard_len + i * V, true, t);
+        Pack<T, V> part[kMaxRanks];
 #pragma unroll
-            for (int j = 0; j < V; ++j) g[j] += t[j];
-        }
+        for (int s = 0; s < kMaxRanks; ++s)       // all loads in flight before the first use
+            if ((uint32_t)s < world) part[s] = load_pack<T, V>(reinterpret_cast<const T *>(grad_rows.p[s]) + i * V);
+#pragma unroll
+        for (int s = 0; s < kMaxRanks; ++s)
+            if ((uint32_t)s < world) {
+#pragma unroll
+                for (int j = 0; j < V; ++j) g[j] += to_f32(part[s].v[j]);
+            }
         load_run<float, V>(master + i * V, true, p);
         load_run<float, V>(dv + i * V, true, v);
         load_run<float, V>(dm + i * V, true, m);

@@ -155,10 +155,11 @@ class GpuContext:
                                              batch_stat, C.byref(lin), C.byref(nrm), train_ctx.learn_rate,
                                              train_ctx.grad_clamp, step & 0xFFFFFFFF))
 
-    def gpu_backward_grads_lp(self, layer, input: Tensor, batch_size: int, batch_stat: int, grad: torch.Tensor,
-                              colsums: torch.Tensor):
+    def gpu_backward_grads_lp(self, layer, input: Tensor, batch_size: int, batch_stat: int, grad, colsums: torch.Tensor):
+        """grad: a torch tensor or a raw device pointer of T [K x N]."""
+        gptr = grad if isinstance(grad, int) else grad.data_ptr()
         self._check(self.lib.sk_backward_grads_lp(self.handle, C.byref(layer.desc()), input.ptr(), input.rows(),
-                                                  batch_size, batch_stat, grad.data_ptr(), colsums.data_ptr()))
+                                                  batch_size, batch_stat, C.c_void_p(gptr), colsums.data_ptr()))
 
     def gpu_apply_update_rows(self, layer, grad: torch.Tensor, row0: int, nrows: int, train_ctx, step: int):
         lin = _optim(train_ctx.optimiser)
@@ -191,14 +192,9 @@ class GpuContext:
                                              step & 0xFFFFFFFF))
 
     # -- fused exchange over peer-mapped buffers (no counterpart in the reference) --
-    def gpu_backward_grads_scatter(self, layer, input: Tensor, batch_size: int, batch_stat: int, peer_stage, world: int,
-                                   rank: int, colsums: torch.Tensor):
-        self._check(self.lib.sk_backward_grads_scatter(self.handle, C.byref(layer.desc()), input.ptr(), input.rows(),
-                                                       batch_size, batch_stat, peer_stage, world, rank, colsums.data_ptr()))
-
-    def gpu_reduce_update_broadcast(self, layer, stage_ptr: int, world: int, rank: int, peer_w, train_ctx, step: int):
+    def gpu_reduce_update_broadcast(self, layer, peer_grad, world: int, rank: int, peer_w, train_ctx, step: int):
         lin = _optim(train_ctx.optimiser)
-        self._check(self.lib.sk_reduce_update_broadcast(self.handle, C.byref(layer.desc()), C.c_void_p(stage_ptr), world, rank,
+        self._check(self.lib.sk_reduce_update_broadcast(self.handle, C.byref(layer.desc()), peer_grad, world, rank,
                                                         peer_w, C.byref(lin), train_ctx.learn_rate, train_ctx.grad_clamp,
                                                         step & 0xFFFFFFFF))
 

@@ -19,11 +19,12 @@ Two exchange schemes:
   (`owned_rows(i)`); the 16-bit weights are complete everywhere.
 
 * "fused" (default for 16-bit blocks on up to 8 GPUs of one node): the same sharding, but without
-  library collectives on the weight path. Every rank maps the other ranks' staging buffers, weight
-  tensors and flag words into its address space (CUDA IPC through torch's tensor sharing). The dW
-  GEMM's epilogue stores each row block straight into the owner's staging buffer over NVLink while the
-  GEMM runs; after a flag handshake the owner adds the staged partials, steps its rows and stores the
-  new 16-bit rows into every rank's weight tensor; a second handshake releases the dX GEMM below.
+  library collectives on the weight path. Every rank keeps one exchange arena (gradient buffer, weight
+  tensor and flag words of every layer) and maps the other ranks' arenas into its address space (CUDA
+  IPC). Each rank writes its 16-bit dW into its own gradient buffer; after a flag handshake ONE kernel
+  per rank pulls the rows it owns out of all gradient buffers over NVLink, adds them, steps them and
+  stores the new 16-bit rows into every rank's weight tensor (reduce-scatter + optimiser + all-gather
+  fused); a second handshake releases the dX GEMM below.
   All flag waits are bounded (SK_ERR_DEVICE_TIMEOUT instead of a hang). Only the small column sums
   still use an NCCL all-reduce.
 
@@ -208,13 +209,13 @@ class DataParallelFFN:
             tci = train_ctx.get_train_context(i)
             if self.fused:
                 W, e = self.world, self.epoch
-                self.ctx.gpu_backward_grads_scatter(layer, x, self.local_batch, self.global_batch, self.p_stage[i], W,
-                                                    self.rank, self.colsums[i])
-                self.ctx.signal_peers(self.p_flag_a[i], W, self.rank, e)       # my partials are in place everywhere
+                self.ctx.gpu_backward_grads_lp(layer, x, self.local_batch, self.global_batch, self.stage_ptr[i],
+                                               self.colsums[i])                 # dW into my arena's gradient buffer
+                self.ctx.signal_peers(self.p_flag_a[i], W, self.rank, e)       # my gradient buffer is complete
                 dist.all_reduce(self.colsums[i], group=self.group)
-                self.ctx.wait_flags(self.flag_ptr[i], W, e)                     # every rank's partials for my rows
-                self.ctx.gpu_reduce_update_broadcast(layer, self.stage_ptr[i], W, self.rank, self.p_recv[i], tci, step)
-                self.ctx.signal_peers(self.p_flag_b[i], W, self.rank, e)       # my rows are in every receive buffer
+                self.ctx.wait_flags(self.flag_ptr[i], W, e)                     # so is everybody else's
+                self.ctx.gpu_reduce_update_broadcast(layer, self.p_stage[i], W, self.rank, self.p_recv[i], tci, step)
+                self.ctx.signal_peers(self.p_flag_b[i], W, self.rank, e)       # my rows are in every weight tensor
                 self.ctx.gpu_apply_vector_update(layer, self.colsums[i], self.global_batch, tci, step)
                 self.ctx.wait_flags(self.flag_ptr[i] + 4 * W, W, e)             # all rows of this layer have arrived
                 self.collectives += 1
