@@ -179,3 +179,74 @@ def test_batchnorm_and_regularisation_sixteen_bit(gpu_ctx, prec):
     tol = 1e-2 if prec == "f16" else 6e-2      # bf16 keeps 8 significant bits
     H.compare_states(gpu_ctx, spec, dnet, onet, tol, skip=("mask",))
     np.testing.assert_allclose(dloss, oloss, rtol=tol)
+
+
+def test_flag_wait_times_out_with_a_status_instead_of_hanging(gpu_ctx):
+    """Failure detection of the fused exchange, without faulting anything: wait on flag words that no
+    rank ever sets. The kernel gives up after its bound (about two seconds), the next synchronize
+    reports SK_ERR_DEVICE_TIMEOUT, and the context stays usable."""
+    import time
+    import torch
+    flags = torch.zeros(4, dtype=torch.int32, device=gpu_ctx.device)
+    t0 = time.time()
+    gpu_ctx.wait_flags(flags.data_ptr(), 2, 1)
+    with pytest.raises(log.NativeError) as e:
+        gpu_ctx.synchronize()
+    assert "status 11" in str(e.value) and time.time() - t0 < 30
+    gpu_ctx.synchronize()                                   # the error word was cleared
+    flags.fill_(7)
+    gpu_ctx.wait_flags(flags.data_ptr(), 4, 7)              # flags already there: returns at once
+    gpu_ctx.synchronize()
+    blk = _block(gpu_ctx)
+    blk.forward(gpu_ctx, _x(gpu_ctx, 6, 12), 6, False, 1)   # kernels still run
+    gpu_ctx.synchronize()
+
+
+def test_host_feeder_round_trip(gpu_ctx):
+    """Pinned host -> device staging and device -> host fetch deliver the bytes they were given."""
+    import torch
+    from soklyn_b200.pipeline import HostFeeder
+    feeder = HostFeeder(gpu_ctx, [(8, 16)], sk.Precision.FP16)
+    host = [torch.arange(128, dtype=torch.float16).reshape(8, 16).pin_memory() * (i + 1) for i in range(3)]
+    out = torch.empty((8, 16), dtype=torch.float16).pin_memory()
+    feeder.stage(1, [host[0]])
+    for s in range(1, 4):
+        slot = s % 2
+        (x,) = feeder.acquire(slot)
+        if s < 3:
+            feeder.stage(1 - slot, [host[s]])
+        feeder.fetch(x, out, 8)
+        feeder.release(slot)
+        feeder.wait_output()
+        assert torch.equal(out, host[s - 1])
+    assert feeder.bytes_h2d == 3 * 256 and feeder.bytes_d2h == 3 * 256
+
+
+@pytest.mark.parametrize("regu,nesterov", [("l1", False), ("l2", True)])
+def test_regularisation_and_nesterov_momentum_match_oracle(gpu_ctx, regu, nesterov):
+    """L1 / L2 regularisation (applied to the weights without the learning rate, src/cuda/kernel/ffn/
+    backward.cu:120-125) and SGD with (Nesterov) momentum over three steps, f32, against the oracle."""
+    from oracle import oracle as ok
+    rng = np.random.default_rng(21)
+    k, n, m = 20, 12, 10
+    w = (rng.standard_normal((k, n)) * 0.3).astype(np.float32)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    t = rng.standard_normal((m, n)).astype(np.float32)
+    coeff = 1e-3
+    reg = sk.Regularisation.l1(coeff) if regu == "l1" else sk.Regularisation.l2(coeff)
+    cfg = sk.LayerInitConfig(sk.Normalisation.LayerNorm, sk.Activation.Identity, reg, 0.0)
+    blk = sk.DenseBlock(gpu_ctx, True, k, n, m, _GivenWeights(w), cfg)
+    oblk = ok.OracleBlock(w, m, norm="layer", act="identity", regu=regu, regu_coeff=coeff)
+    xd, td = sk.Tensor.from_cpu_vector(gpu_ctx, x, x.shape), sk.Tensor.from_cpu_vector(gpu_ctx, t, t.shape)
+    opt = sk.Optimiser.SGD(0.9, nesterov)
+    for step in range(1, 4):
+        blk.forward(gpu_ctx, xd, m, False, step)
+        blk.compute_loss(gpu_ctx, td, sk.LossConfig(sk.LossFunc.MeanSquareLoss, sk.Activation.Tanh))
+        blk.backward_output(gpu_ctx, xd, sk.TrainContext(opt, opt, m, 0.05, 0.5), step)     # clamp 0.5 on the update
+        oblk.forward(x, m, False, step)
+        oblk.compute_loss(t, "mse", "tanh")
+        oblk.backward_output(x, ok.TrainContext(ok.sgd(0.9, nesterov), ok.sgd(0.9, nesterov), m, 0.05, 0.5), step)
+    for name, got in (("w", blk.get_weights()), ("b", blk.get_biases()), ("dv_w", blk.get_dv_weights()),
+                      ("norm_w", blk.get_norm_weights()), ("norm_b", blk.get_norm_biases())):
+        e = H.relerr(got.download(gpu_ctx).reshape(-1), getattr(oblk, name).reshape(-1))
+        assert e <= 2e-5, f"{name}: {e:.2e}"
