@@ -26,10 +26,11 @@ import torch  # noqa: E402
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the three GEMM classes of the
 # default workload, from the ncu capture summarised in profiles/wide_ffn_step_ncu_full_b2048.md. That
-# capture ran the same network at batch 2048 (a full-size capture would hold too much device memory
-# for ncu's save/restore); the figures are its per-launch averages times 4, i.e. scaled by the rows
-# processed, which over-counts the weight operand (read once whatever the batch) by < 10 %.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = {"gemm_forward": 4 * 292.5e6, "gemm_dx": 4 * 953.4e6, "gemm_dw": 4 * 1914.0e6}
+# capture ran the same network at batch 2048 (a full-size capture would hold too much device memory for
+# ncu's save/restore). Scaled to batch 8192 as: measured bytes + 3 x the bytes that grow with the batch
+# (activations in and out of the GEMM and its epilogue); weights, and for dW the 26 B per parameter of the
+# fused optimiser step, are the same at any batch. Averages over the launches of a class.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {"gemm_forward": 545e6, "gemm_dx": 3017e6, "gemm_dw": 2166e6}
 
 
 def measured_peaks():
@@ -242,7 +243,7 @@ def run_ours(args):
             "roofline": {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": peaks["tflops"],
                          "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
                          "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get(top) if spec.cfg == 4 and world == 1 else None,
-                         "traffic_note": "bytes per launch, ncu capture at batch 2048 scaled x4 (see profiles/)",
+                         "traffic_note": "bytes per launch: ncu capture at batch 2048, batch-proportional part scaled to 8192 (see profiles/)",
                          "peak_source": peaks["source"] + " (bf16 matmul, sustained)",
                          "launches": int(n_l), "ms_per_launch": t_ms / max(1, n_l)},
             "kernel_ms_per_step": {k: v[1] / args.steps for k, v in prof.items()},
