@@ -245,6 +245,9 @@ template <typename T, int ACT = -1, int NORM = -1> struct EpiHidden {
         core<V>(row, col0, acc, pd, pa, mk, xv, nw, rs);
     }
 
+    // the specialised kernels are small enough to be unrolled with two passes of loads in flight
+    static constexpr bool kPingPong = ACT >= 0 && NORM >= 0;
+    static constexpr int kGroup = kPingPong ? 2 : 1;
     struct Cols { float nw[8], rs[8]; };
     struct Pre { Pack<T, 8> pd, pa, mk, xv; T rrow; };
     __device__ __forceinline__ void cols(uint32_t col0, Cols &c) const {
@@ -322,6 +325,7 @@ template <typename T, int KIND = -1, int REGU = -1> struct EpiWeightUpdate {
         }
     }
 
+    static constexpr bool kPingPong = KIND >= 0 && REGU >= 0;
     struct Cols {};
     struct Pre { Pack<float, 8> p, v, m; };
     __device__ __forceinline__ void cols(uint32_t, Cols &) const {}

@@ -40,6 +40,13 @@ template <int BN> struct TcShape {
     static constexpr int kSmemBytes = 1024 /*alignment slack*/ + kStages * kStageBytes + kEpiBufBytes + kBarBytes;
 };
 
+// Passes of the epilogue whose loads are in flight together: functors may declare kGroup (1, 2 or 4).
+template <class Epi, class = void> struct EpiGroup { static constexpr int value = 1; };
+template <class Epi> struct EpiGroup<Epi, decltype((void)Epi::kGroup)> { static constexpr int value = Epi::kGroup; };
+// Functors whose body is small enough to exist four times declare kPingPong = true.
+template <class Epi, class = void> struct EpiPingPong { static constexpr bool value = false; };
+template <class Epi> struct EpiPingPong<Epi, decltype((void)Epi::kPingPong)> { static constexpr bool value = Epi::kPingPong; };
+
 enum : int { kTcErrProducer = 1, kTcErrMma = 2, kTcErrEpilogue = 3 };
 
 // Tile order. Tiles are walked in groups of group_n tile-columns (8 by default), row-major inside a group, so
@@ -165,44 +172,84 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const uint32_t m0 = mi * kTcBM, n0 = ni * BN;
             if (!tc::mbar_wait(&tmem_full[acc], acc_phase)) { ok = false; break; }
             tc::tc_fence_after_sync();
+            // Runs of a 32-column chunk: pass p covers rows 8p + lane/4, columns 8*(lane%4) .. +8. The
+            // fast path (128-bit accesses, a full run of 8 columns) keeps the global loads of the NEXT
+            // group of G passes in flight while the current group is finished, also across chunks, so
+            // that only the first group of a tile waits for memory with nothing else to do.
+            // Generic functors (every activation and normalisation case in one body) run the group loop
+            // rolled, because their body must exist once or the kernel outgrows the instruction cache;
+            // the price is that handing `nxt` over to `cur` at the end of an iteration waits for the
+            // loads. Specialised functors are small enough to unroll the loop (4 bodies): two register
+            // sets then swap roles and nothing waits before the data is needed.
+            constexpr int G = EpiGroup<Epi>::value, NQ = 4 / G;
+            constexpr bool kPing = EpiPingPong<Epi>::value;
+            static_assert(!kPing || NQ % 2 == 0, "ping-pong needs an even number of groups per chunk");
+            const uint32_t c_end = (half + 1) * (BN / 2);
+            const uint32_t cc = (lane & 3) * 8;
+            const uint32_t row_base = m0 + quarter * 32 + (lane >> 2);
+            typename Epi::Cols cols, cols_n;
+            typename Epi::Pre pre[2][G];              // [0]: current group at the start of a chunk
+            bool have = false;                        // pre[0] / cols already hold this chunk's first group
 #pragma unroll 1
-            for (uint32_t c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32) {
+            for (uint32_t c0 = half * (BN / 2); c0 < c_end; c0 += 32) {
                 if (n0 + c0 >= N) break;              // uniform per warp
-                // runs of this chunk: pass p covers rows 8p + lane/4, columns 8*(lane%4) .. +8
-                const uint32_t cc = (lane & 3) * 8, col = n0 + c0 + cc;
-                const uint32_t row_base = m0 + quarter * 32 + (lane >> 2);
+                const uint32_t col = n0 + c0 + cc;
                 const bool col_ok = col < N;
                 const uint32_t ncols = col_ok ? min(8u, N - col) : 0u;
-                // The fast path needs 128-bit accesses and a full run of 8 columns; everything
-                // else (ragged right edge, unaligned tensors) goes through run<8>.
-                const bool fast = epi.vec_ok && ncols == 8;
-                // One run ahead: the loads of pass p+1 are in flight while pass p is finished. The
-                // pass loop is deliberately not unrolled: the epilogue body (every activation and
-                // normalisation case) must exist once, or the kernel outgrows the instruction cache.
-                typename Epi::Cols cols;
-                typename Epi::Pre cur, nxt;
-                if (fast) {
+                const bool fast = epi.vec_ok && ncols == 8;   // else: ragged right edge, unaligned tensors
+                if (fast && !have) {
                     epi.cols(col, cols);
-                    if (row_base < M) epi.prefetch(row_base, col, cur);
+#pragma unroll
+                    for (int g = 0; g < G; ++g)
+                        if (row_base + 8 * g < M) epi.prefetch(row_base + 8 * g, col, pre[0][g]);
                 }
                 float v[32];
                 tc::tmem_ld_32x32(tmem_base + ((quarter * 32) << 16) + acc * BN + c0, v);
 #pragma unroll
                 for (int j = 0; j < 32; ++j) buf[lane * 33 + j] = v[j];
                 __syncwarp();
-#pragma unroll 1
-                for (int p = 0; p < 4; ++p) {
-                    const uint32_t rr = p * 8 + (lane >> 2), row = m0 + quarter * 32 + rr;
-                    if (fast && p < 3 && row + 8 < M) epi.prefetch(row + 8, col, nxt);
-                    float r[8];
+                bool have_n = false;
+                auto group = [&](int q, typename Epi::Pre (&cur)[G], typename Epi::Pre (&nxt)[G]) {
+                    if (fast) {
+                        if (q + 1 < NQ) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) r[j] = buf[rr * 33 + cc + j];
-                    if (col_ok && row < M) {
-                        if (fast) epi.finish(row, col, r, cur, cols);
-                        else epi.template run<8>(row, col, r, ncols);
+                            for (int g = 0; g < G; ++g) {
+                                const uint32_t row = row_base + 8 * ((q + 1) * G + g);
+                                if (row < M) epi.prefetch(row, col, nxt[g]);
+                            }
+                        } else if (c0 + 32 < c_end && col + 40 <= N) {   // first group of the next chunk
+                            epi.cols(col + 32, cols_n);
+#pragma unroll
+                            for (int g = 0; g < G; ++g)
+                                if (row_base + 8 * g < M) epi.prefetch(row_base + 8 * g, col + 32, nxt[g]);
+                            have_n = true;
+                        }
                     }
-                    cur = nxt;
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        const uint32_t rr = (q * G + g) * 8 + (lane >> 2), row = m0 + quarter * 32 + rr;
+                        float r[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) r[j] = buf[rr * 33 + cc + j];
+                        if (col_ok && row < M) {
+                            if (fast) epi.finish(row, col, r, cur[g], cols);
+                            else epi.template run<8>(row, col, r, ncols);
+                        }
+                    }
+                };
+                if constexpr (kPing) {
+#pragma unroll
+                    for (int q = 0; q < NQ; ++q) group(q, pre[q & 1], pre[(q + 1) & 1]);
+                } else {
+#pragma unroll 1
+                    for (int q = 0; q < NQ; ++q) {
+                        group(q, pre[0], pre[1]);
+#pragma unroll
+                        for (int g = 0; g < G; ++g) pre[0][g] = pre[1][g];
+                    }
                 }
+                if (have_n) cols = cols_n;
+                have = have_n;
                 __syncwarp();
             }
             tc::tc_fence_before_sync();
