@@ -36,6 +36,11 @@ struct sk_ctx {
     void *encode_tiled = nullptr;          // cuTensorMapEncodeTiled, resolved through the runtime
     std::map<std::tuple<const void *, uint64_t, uint64_t, uint64_t, uint32_t, uint32_t>, CUtensorMap> tmaps;
     uint64_t tc_launches = 0;
+    // Column sums handed from the dX epilogue to the weight update of the same layer. Only inside
+    // sk_ffn_backward (nothing can touch the tensors or the workspace in between there).
+    bool in_ffn_backward = false;
+    const void *fused_colsum_key = nullptr;   // d_prenorm of the layer whose partial sums sit in the workspace
+    uint32_t fused_colsum_groups = 0, fused_colsum_batch = 0;
     // optional per-class event timing
     bool profiling = false;
     std::vector<cudaEvent_t> ev_pool;      // pairs: [2i] start, [2i+1] stop
@@ -164,6 +169,7 @@ cudaError_t run_gemm(sk_ctx *c, uint32_t dtype, const TA *A, size_t lda, const T
 }
 
 inline bool aligned16(const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
+constexpr uint32_t kColsumFold = 8;   // slabs the per-32-row column sums of the dX epilogue are folded into
 
 Optim make_optim(const sk_optim *o, uint32_t step) {
     Optim r{};
@@ -309,6 +315,20 @@ int hidden_error_impl(sk_ctx *c, const sk_dense *cur, const sk_dense *next, uint
     const uint32_t ec = next->N;
     const T *dy = f32 ? (const T *)next->d_prenorm : (const T *)next->d_prenorm_lp;
     const T *wn = f32 ? (const T *)master_of<T>(next->master_w, next->w) : (const T *)next->w;
+    // Column sums for the weight update that follows, taken in the epilogue when that update is
+    // certain to be the next call, the tensor-core kernel runs and the partial sums fit.
+    epi.colsum_partial = nullptr; epi.colsum_groups = 0;
+    c->fused_colsum_key = nullptr;
+    const bool specialised = !f32 && ((cur->act == SK_ACT_SILU && cur->norm == SK_NORM_RMS) ||
+                                      (cur->act == SK_ACT_MISH && cur->norm == SK_NORM_LAYER));
+    if (c->in_ffn_backward && specialised && epi.vec_ok && tc_eligible(c, cur->dtype, dy, ec, wn, ec)) {
+        const uint32_t groups = (batch + 31) / 32;
+        const size_t need = ((size_t)groups + kColsumFold) * 3 * cur->N * sizeof(float);
+        if (need <= c->workspace_bytes) {
+            epi.colsum_partial = (float *)c->workspace; epi.colsum_groups = groups;
+            c->fused_colsum_key = cur->d_prenorm; c->fused_colsum_groups = groups; c->fused_colsum_batch = batch;
+        }
+    }
     ProfScope ps(c, SK_PROF_GEMM_DX);
     cudaError_t e;
     // kernels specialised for the activation / normalisation pairs of the wide and the classifier networks
@@ -325,6 +345,7 @@ int hidden_error_impl(sk_ctx *c, const sk_dense *cur, const sk_dense *next, uint
         e = run_gemm<T, T, true, false>(c, cur->dtype, dy, ec, wn, ec, batch, cur->N, ec, epi);
     }
     int rc = check_cuda(c, e, "hidden error gemm");
+    if (rc) c->fused_colsum_key = nullptr;
     c->launches++;
     return rc;
 }
@@ -370,9 +391,26 @@ int backward_update_impl(sk_ctx *c, const sk_dense *L, const void *x, uint32_t b
     const Optim lin = make_optim(lin_, step), nrm = make_optim(nrm_, step);
     const Hyper hyp{lr, clamp, 1.0f / (float)batch, L->regu, L->regu_coeff};
     int rc = SK_OK;
-    const uint32_t nblocks = launch_colsum_partial(c, L, batch, &rc);
-    if (rc) return rc;
-    if ((rc = vector_update_launch<T>(c, L, (const float *)c->workspace, nblocks, lin, nrm, hyp))) return rc;
+    if (c->fused_colsum_key && c->fused_colsum_key == L->d_prenorm && c->fused_colsum_batch == batch) {
+        // the dX epilogue left one slab of sums per 32 rows in the workspace: fold them, then step
+        const uint32_t groups = c->fused_colsum_groups, per = (groups + kColsumFold - 1) / kColsumFold;
+        const uint32_t slabs = (groups + per - 1) / per;
+        float *folded = (float *)c->workspace + (size_t)groups * 3 * L->N;
+        c->fused_colsum_key = nullptr;
+        {
+            ProfScope ps(c, SK_PROF_COLSUM);
+            colsum_fold_kernel<<<dim3((3 * L->N + 255) / 256, slabs), 256, 0, c->stream>>>((const float *)c->workspace, folded,
+                                                                                          L->N, groups, per);
+            c->launches++;
+            if ((rc = check_cuda(c, cudaGetLastError(), "column sums (fold)"))) return rc;
+        }
+        if ((rc = vector_update_launch<T>(c, L, folded, slabs, lin, nrm, hyp))) return rc;
+    } else {
+        c->fused_colsum_key = nullptr;
+        const uint32_t nblocks = launch_colsum_partial(c, L, batch, &rc);
+        if (rc) return rc;
+        if ((rc = vector_update_launch<T>(c, L, (const float *)c->workspace, nblocks, lin, nrm, hyp))) return rc;
+    }
     const bool f32 = L->dtype == SK_F32;
     EpiWeightUpdate<T> epi{};
     epi.w = (T *)L->w; epi.master = master_of<T>(L->master_w, L->w); epi.dv = L->dv_w; epi.dm = L->dm_w;
@@ -767,12 +805,16 @@ int sk_ffn_backward(sk_ctx *c, const sk_dense *const *layers, uint32_t n, const 
     if (rc) return rc;
     const void *in = input_of(last, rows);
     if ((rc = sk_backward_update(c, layers[last], in, rows, batch, &lin[last], &nrm[last], lr, clamp, step))) return rc;
-    for (uint32_t i = last; i-- > 0;) {
-        if ((rc = sk_hidden_error(c, layers[i], layers[i + 1], batch, batch))) return rc;
+    for (uint32_t i = last; i-- > 0 && rc == SK_OK;) {
+        c->in_ffn_backward = true;    // the update of layer i follows its delta directly: sums may be handed over
+        rc = sk_hidden_error(c, layers[i], layers[i + 1], batch, batch);
+        c->in_ffn_backward = false;
+        if (rc) break;
         in = input_of(i, rows);
-        if ((rc = sk_backward_update(c, layers[i], in, rows, batch, &lin[i], &nrm[i], lr, clamp, step))) return rc;
+        rc = sk_backward_update(c, layers[i], in, rows, batch, &lin[i], &nrm[i], lr, clamp, step);
     }
-    return SK_OK;
+    c->fused_colsum_key = nullptr;
+    return rc;
 }
 
 int sk_backward_grads(sk_ctx *c, const sk_dense *L, const void *x, uint32_t x_rows, uint32_t batch, float *dw,

@@ -162,6 +162,13 @@ template <typename T, int ACT = -1, int NORM = -1> struct EpiHidden {
     uint32_t N, norm, act;
     float leaky, inv_n, inv_m;
     bool vec_ok;
+    // Optional: column sums of d_prenorm, d_norm_w and d_norm_b per group of 32 rows, written as
+    // partial[group][which][col] while the values are in registers, so that the weight-update call
+    // that follows need not read the three tensors again. Only with vec_ok and on the tensor-core
+    // kernel (every element then goes through finish()).
+    float *colsum_partial;
+    uint32_t colsum_groups;
+    struct Acc { float dp[8], gw[8], gb[8]; };
 
     __device__ __forceinline__ uint32_t A() const { return ACT >= 0 ? (uint32_t)ACT : act; }
     __device__ __forceinline__ uint32_t Nm() const { return NORM >= 0 ? (uint32_t)NORM : norm; }
@@ -186,7 +193,7 @@ template <typename T, int ACT = -1, int NORM = -1> struct EpiHidden {
     template <int V>
     __device__ __forceinline__ void core(uint32_t row, uint32_t col0, const float (&acc)[V], const float (&pd)[V],
                                          const float (&pa)[V], const float (&mk)[V], const float (&xv)[V],
-                                         const float (&nw)[V], const float (&rs)[V]) const {
+                                         const float (&nw)[V], const float (&rs)[V], Acc *sums = nullptr) const {
         const size_t idx = (size_t)row * N + col0;
         float gr[V], dp[V], gw[V], gb[V];
 #pragma unroll
@@ -220,6 +227,12 @@ template <typename T, int ACT = -1, int NORM = -1> struct EpiHidden {
         store_run<float, V>(d_norm_w + idx, true, gw);
         store_run<float, V>(d_norm_b + idx, true, gb);
         if (d_prenorm_lp) store_run<T, V>(d_prenorm_lp + idx, true, dp);
+        if constexpr (V == 8) {
+            if (sums && colsum_partial) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { sums->dp[j] += dp[j]; sums->gw[j] += gw[j]; sums->gb[j] += gb[j]; }
+            }
+        }
     }
 
     template <int V>
@@ -250,6 +263,31 @@ template <typename T, int ACT = -1, int NORM = -1> struct EpiHidden {
     static constexpr int kGroup = kPingPong ? 2 : 1;
     struct Cols { float nw[8], rs[8]; };
     struct Pre { Pack<T, 8> pd, pa, mk, xv; T rrow; };
+    static constexpr bool kHasAcc = ACT >= 0 && NORM >= 0;   // the generic functor has no registers to spare
+    __device__ __forceinline__ void acc_init(Acc &a) const {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { a.dp[j] = 0.0f; a.gw[j] = 0.0f; a.gb[j] = 0.0f; }
+    }
+    // Called by all 32 lanes of the warp after the four passes of a chunk: lanes that hold the same
+    // columns (equal lane % 4) add their rows up, lanes 0-3 store the sums of the 32-row group.
+    __device__ __forceinline__ void acc_flush(Acc &a, uint32_t group, uint32_t col0, uint32_t lane, bool valid) const {
+        if (!colsum_partial) return;
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                a.dp[j] += __shfl_xor_sync(0xffffffffu, a.dp[j], off);
+                if (Nm() >= 1) a.gw[j] += __shfl_xor_sync(0xffffffffu, a.gw[j], off);
+                if (Nm() >= 2) a.gb[j] += __shfl_xor_sync(0xffffffffu, a.gb[j], off);
+            }
+        }
+        if (valid && lane < 4 && group < colsum_groups) {
+            float *base = colsum_partial + (size_t)group * 3 * N + col0;
+            store_run<float, 8>(base, true, a.dp);
+            store_run<float, 8>(base + N, true, a.gw);
+            store_run<float, 8>(base + 2 * (size_t)N, true, a.gb);
+        }
+    }
     __device__ __forceinline__ void cols(uint32_t col0, Cols &c) const {
         if (Nm()) load_run<float, 8>(norm_w + col0, true, c.nw);
         if (Nm() == 3) load_run<T, 8>(rstd + col0, true, c.rs);
@@ -264,6 +302,14 @@ template <typename T, int ACT = -1, int NORM = -1> struct EpiHidden {
         if (Nm() == 1 || Nm() == 2) p.rrow = rstd[row];
     }
     __device__ __forceinline__ void finish(uint32_t row, uint32_t col0, const float (&acc)[8], const Pre &p, const Cols &c) const {
+        finish_impl(row, col0, acc, p, c, nullptr);
+    }
+    __device__ __forceinline__ void finish(uint32_t row, uint32_t col0, const float (&acc)[8], const Pre &p, const Cols &c,
+                                           Acc &sums) const {
+        finish_impl(row, col0, acc, p, c, &sums);
+    }
+    __device__ __forceinline__ void finish_impl(uint32_t row, uint32_t col0, const float (&acc)[8], const Pre &p, const Cols &c,
+                                                Acc *sums) const {
         float pd[8], pa[8], mk[8], xv[8], rs[8];
         unpack<T, 8>(p.pd, pd);
         unpack<T, 8>(p.pa, pa);
@@ -277,7 +323,7 @@ template <typename T, int ACT = -1, int NORM = -1> struct EpiHidden {
 #pragma unroll
             for (int j = 0; j < 8; ++j) rs[j] = r;
         }
-        core<8>(row, col0, acc, pd, pa, mk, xv, c.nw, rs);
+        core<8>(row, col0, acc, pd, pa, mk, xv, c.nw, rs, sums);
     }
 };
 

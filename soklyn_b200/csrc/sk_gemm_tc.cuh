@@ -19,6 +19,8 @@
 // error code and leaves.
 #pragma once
 
+#include <type_traits>
+
 #include "sk_epilogue.cuh"
 #include "sk_tc_ptx.cuh"
 
@@ -43,6 +45,10 @@ template <int BN> struct TcShape {
 // Passes of the epilogue whose loads are in flight together: functors may declare kGroup (1, 2 or 4).
 template <class Epi, class = void> struct EpiGroup { static constexpr int value = 1; };
 template <class Epi> struct EpiGroup<Epi, decltype((void)Epi::kGroup)> { static constexpr int value = Epi::kGroup; };
+// Functors that keep running sums over the passes of a chunk declare kHasAcc, Acc, acc_init, acc_flush
+// and take the accumulator as the last argument of finish().
+template <class Epi, class = void> struct EpiAcc { static constexpr bool value = false; struct type {}; };
+template <class Epi> struct EpiAcc<Epi, std::enable_if_t<Epi::kHasAcc>> { static constexpr bool value = true; using type = typename Epi::Acc; };
 // Functors whose body is small enough to exist four times declare kPingPong = true.
 template <class Epi, class = void> struct EpiPingPong { static constexpr bool value = false; };
 template <class Epi> struct EpiPingPong<Epi, decltype((void)Epi::kPingPong)> { static constexpr bool value = Epi::kPingPong; };
@@ -209,6 +215,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 for (int j = 0; j < 32; ++j) buf[lane * 33 + j] = v[j];
                 __syncwarp();
                 bool have_n = false;
+                typename EpiAcc<Epi>::type sums;
+                if constexpr (EpiAcc<Epi>::value) epi.acc_init(sums);
                 auto group = [&](int q, typename Epi::Pre (&cur)[G], typename Epi::Pre (&nxt)[G]) {
                     if (fast) {
                         if (q + 1 < NQ) {
@@ -232,8 +240,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
                         for (int j = 0; j < 8; ++j) r[j] = buf[rr * 33 + cc + j];
                         if (col_ok && row < M) {
-                            if (fast) epi.finish(row, col, r, cur[g], cols);
-                            else epi.template run<8>(row, col, r, ncols);
+                            if (fast) {
+                                if constexpr (EpiAcc<Epi>::value) epi.finish(row, col, r, cur[g], cols, sums);
+                                else epi.finish(row, col, r, cur[g], cols);
+                            } else {
+                                epi.template run<8>(row, col, r, ncols);
+                            }
                         }
                     }
                 };
@@ -248,6 +260,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         for (int g = 0; g < G; ++g) pre[0][g] = pre[1][g];
                     }
                 }
+                if constexpr (EpiAcc<Epi>::value) epi.acc_flush(sums, (m0 + quarter * 32) / 32, col, lane, fast);
                 if (have_n) cols = cols_n;
                 have = have_n;
                 __syncwarp();

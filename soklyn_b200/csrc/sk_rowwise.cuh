@@ -318,6 +318,25 @@ colsum_partial_kernel(const float *__restrict__ d_prenorm, const float *__restri
     }
 }
 
+// Folds `nin` partial slabs [3 x N] into gridDim.y slabs (slab y takes inputs y*per .. y*per+per-1), in a
+// fixed order: used when the slabs come from the dX epilogue, one per 32 rows.
+__global__ void colsum_fold_kernel(const float *__restrict__ in, float *__restrict__ out, uint32_t N, uint32_t nin,
+                                   uint32_t per) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= 3 * N) return;
+    const uint32_t b0 = blockIdx.y * per, b1 = min(nin, b0 + per);
+    float t0 = 0.0f, t1 = 0.0f, t2 = 0.0f, t3 = 0.0f;
+    uint32_t b = b0;
+    for (; b + 4 <= b1; b += 4) {
+        t0 += in[(size_t)b * 3 * N + i];
+        t1 += in[(size_t)(b + 1) * 3 * N + i];
+        t2 += in[(size_t)(b + 2) * 3 * N + i];
+        t3 += in[(size_t)(b + 3) * 3 * N + i];
+    }
+    for (; b < b1; ++b) t0 += in[(size_t)b * 3 * N + i];
+    out[(size_t)blockIdx.y * 3 * N + i] = (t0 + t1) + (t2 + t3);
+}
+
 // Stage 2 without update: colsums[which][col] = sum of partials (raw, still x512).
 __global__ void colsum_final_kernel(const float *__restrict__ partial, float *__restrict__ colsums, uint32_t N,
                                     uint32_t nblocks) {
