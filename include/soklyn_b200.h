@@ -98,8 +98,13 @@ void sk_ctx_destroy(sk_ctx *ctx);
 int sk_ctx_set_stream(sk_ctx *ctx, void *stream);
 /* Context options (no counterpart). SK_OPTION_GEMM_ENGINE: 0 = automatic (tcgen05 tensor-core
  * kernel for 16-bit operands whose row pitches are multiples of 16 bytes, FFMA kernel
- * otherwise), 1 = FFMA kernel only. */
-enum { SK_OPTION_GEMM_ENGINE = 0 };
+ * otherwise), 1 = FFMA kernel only.
+ * SK_OPTION_COLSUM_HANDOVER: 1 = sk_hidden_error may take the column sums of the layer's d_prenorm /
+ * d_norm_w / d_norm_b in its GEMM epilogue and hand them, through the workspace, to the next call if
+ * that call is sk_backward_update / sk_backward_grads_lp for the same layer and batch (any other call
+ * drops them). The caller promises not to modify those three tensors between the two calls. Off by
+ * default; sk_ffn_backward always does this internally, where nothing can come in between. */
+enum { SK_OPTION_GEMM_ENGINE = 0, SK_OPTION_COLSUM_HANDOVER = 1 };
 int sk_ctx_set_option(sk_ctx *ctx, uint32_t option, uint32_t value);
 /* Grow the scratch workspace; never called implicitly. */
 int sk_ctx_reserve(sk_ctx *ctx, size_t workspace_bytes);

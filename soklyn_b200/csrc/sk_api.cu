@@ -39,6 +39,7 @@ struct sk_ctx {
     // Column sums handed from the dX epilogue to the weight update of the same layer. Only inside
     // sk_ffn_backward (nothing can touch the tensors or the workspace in between there).
     bool in_ffn_backward = false;
+    bool colsum_handover = false;             // SK_OPTION_COLSUM_HANDOVER
     const void *fused_colsum_key = nullptr;   // d_prenorm of the layer whose partial sums sit in the workspace
     uint32_t fused_colsum_groups = 0, fused_colsum_batch = 0;
     // optional per-class event timing
@@ -321,7 +322,7 @@ int hidden_error_impl(sk_ctx *c, const sk_dense *cur, const sk_dense *next, uint
     c->fused_colsum_key = nullptr;
     const bool specialised = !f32 && ((cur->act == SK_ACT_SILU && cur->norm == SK_NORM_RMS) ||
                                       (cur->act == SK_ACT_MISH && cur->norm == SK_NORM_LAYER));
-    if (c->in_ffn_backward && specialised && epi.vec_ok && tc_eligible(c, cur->dtype, dy, ec, wn, ec)) {
+    if ((c->in_ffn_backward || c->colsum_handover) && specialised && epi.vec_ok && tc_eligible(c, cur->dtype, dy, ec, wn, ec)) {
         const uint32_t groups = (batch + 31) / 32;
         const size_t need = ((size_t)groups + kColsumFold) * 3 * cur->N * sizeof(float);
         if (need <= c->workspace_bytes) {
@@ -372,6 +373,27 @@ uint32_t launch_colsum_partial(sk_ctx *c, const sk_dense *L, uint32_t batch, int
     return *rc ? 0 : gy;
 }
 
+// If the dX epilogue of this layer left per-32-row column sums in the workspace, folds them into
+// kColsumFold slabs and returns those; otherwise runs the column-sum kernel over the three tensors.
+const float *column_sum_slabs(sk_ctx *c, const sk_dense *L, uint32_t batch, uint32_t *nslabs, int *rc) {
+    if (c->fused_colsum_key && c->fused_colsum_key == L->d_prenorm && c->fused_colsum_batch == batch) {
+        const uint32_t groups = c->fused_colsum_groups, per = (groups + kColsumFold - 1) / kColsumFold;
+        const uint32_t slabs = (groups + per - 1) / per;
+        float *folded = (float *)c->workspace + (size_t)groups * 3 * L->N;
+        c->fused_colsum_key = nullptr;
+        ProfScope ps(c, SK_PROF_COLSUM);
+        colsum_fold_kernel<<<dim3((3 * L->N + 255) / 256, slabs), 256, 0, c->stream>>>((const float *)c->workspace, folded,
+                                                                                      L->N, groups, per);
+        c->launches++;
+        *rc = check_cuda(c, cudaGetLastError(), "column sums (fold)");
+        *nslabs = slabs;
+        return folded;
+    }
+    c->fused_colsum_key = nullptr;
+    *nslabs = launch_colsum_partial(c, L, batch, rc);
+    return (const float *)c->workspace;
+}
+
 template <typename T>
 int vector_update_launch(sk_ctx *c, const sk_dense *L, const float *partial, uint32_t nblocks, const Optim &lin,
                          const Optim &nrm, const Hyper &hyp) {
@@ -391,26 +413,10 @@ int backward_update_impl(sk_ctx *c, const sk_dense *L, const void *x, uint32_t b
     const Optim lin = make_optim(lin_, step), nrm = make_optim(nrm_, step);
     const Hyper hyp{lr, clamp, 1.0f / (float)batch, L->regu, L->regu_coeff};
     int rc = SK_OK;
-    if (c->fused_colsum_key && c->fused_colsum_key == L->d_prenorm && c->fused_colsum_batch == batch) {
-        // the dX epilogue left one slab of sums per 32 rows in the workspace: fold them, then step
-        const uint32_t groups = c->fused_colsum_groups, per = (groups + kColsumFold - 1) / kColsumFold;
-        const uint32_t slabs = (groups + per - 1) / per;
-        float *folded = (float *)c->workspace + (size_t)groups * 3 * L->N;
-        c->fused_colsum_key = nullptr;
-        {
-            ProfScope ps(c, SK_PROF_COLSUM);
-            colsum_fold_kernel<<<dim3((3 * L->N + 255) / 256, slabs), 256, 0, c->stream>>>((const float *)c->workspace, folded,
-                                                                                          L->N, groups, per);
-            c->launches++;
-            if ((rc = check_cuda(c, cudaGetLastError(), "column sums (fold)"))) return rc;
-        }
-        if ((rc = vector_update_launch<T>(c, L, folded, slabs, lin, nrm, hyp))) return rc;
-    } else {
-        c->fused_colsum_key = nullptr;
-        const uint32_t nblocks = launch_colsum_partial(c, L, batch, &rc);
-        if (rc) return rc;
-        if ((rc = vector_update_launch<T>(c, L, (const float *)c->workspace, nblocks, lin, nrm, hyp))) return rc;
-    }
+    uint32_t nslabs = 0;
+    const float *slabs = column_sum_slabs(c, L, batch, &nslabs, &rc);
+    if (rc) return rc;
+    if ((rc = vector_update_launch<T>(c, L, slabs, nslabs, lin, nrm, hyp))) return rc;
     const bool f32 = L->dtype == SK_F32;
     EpiWeightUpdate<T> epi{};
     epi.w = (T *)L->w; epi.master = master_of<T>(L->master_w, L->w); epi.dv = L->dv_w; epi.dm = L->dm_w;
@@ -462,9 +468,10 @@ template <typename T>
 int backward_grads_lp_impl(sk_ctx *c, const sk_dense *L, const void *x, uint32_t batch, uint32_t batch_stat, void *g,
                            float *colsums) {
     int rc = SK_OK;
-    const uint32_t nblocks = launch_colsum_partial(c, L, batch, &rc);
+    uint32_t nblocks = 0;
+    const float *slabs = column_sum_slabs(c, L, batch, &nblocks, &rc);
     if (rc) return rc;
-    colsum_final_kernel<<<(3 * L->N + 255) / 256, 256, 0, c->stream>>>((const float *)c->workspace, colsums, L->N, nblocks);
+    colsum_final_kernel<<<(3 * L->N + 255) / 256, 256, 0, c->stream>>>(slabs, colsums, L->N, nblocks);
     c->launches++;
     if ((rc = check_cuda(c, cudaGetLastError(), "column sums (final)"))) return rc;
     EpiStoreScaled<T> epi{(T *)g, L->N, 1.0f / (float)batch_stat, L->N % 8 == 0 && aligned16(g)};
@@ -624,6 +631,7 @@ int sk_ctx_set_stream(sk_ctx *c, void *stream) {
 
 int sk_ctx_reserve(sk_ctx *c, size_t workspace_bytes) {
     if (!c) return SK_ERR_NULL_POINTER;
+    c->fused_colsum_key = nullptr;   // column sums handed over by sk_hidden_error are for the very next call only
     if (workspace_bytes <= c->workspace_bytes) return SK_OK;
     cudaSetDevice(c->device);
     cudaStreamSynchronize(c->stream);
@@ -652,6 +660,11 @@ int sk_sync(sk_ctx *c) {
 int sk_ctx_set_option(sk_ctx *c, uint32_t option, uint32_t value) {
     if (!c) return SK_ERR_NULL_POINTER;
     if (option == SK_OPTION_GEMM_ENGINE && value <= 1) { c->gemm_engine = value; return SK_OK; }
+    if (option == SK_OPTION_COLSUM_HANDOVER && value <= 1) {
+        c->colsum_handover = value != 0;
+        c->fused_colsum_key = nullptr;
+        return SK_OK;
+    }
     return fail(c, SK_ERR_INVALID_CONFIGURATION, "unknown option %u / value %u", option, value);
 }
 
@@ -720,6 +733,7 @@ int sk_dense_forward(sk_ctx *c, const sk_dense *L, const void *x, uint32_t x_row
     int rc = check_layer(c, L, false);
     if (rc) return rc;
     if (!x) return fail(c, SK_ERR_NULL_POINTER, "input pointer is NULL");
+    c->fused_colsum_key = nullptr;   // column sums handed over by sk_hidden_error are for the very next call only
     if ((rc = check_batch(c, L, x_rows, batch))) return rc;
     return SK_DISPATCH(L->dtype, forward_impl, c, L, x, batch, use_dropout, step, row_offset);
 }
@@ -729,6 +743,7 @@ int sk_output_error(sk_ctx *c, const sk_dense *L, const void *target, uint32_t t
     int rc = check_layer(c, L, true);
     if (rc) return rc;
     if (!target) return fail(c, SK_ERR_NULL_POINTER, "target pointer is NULL");
+    c->fused_colsum_key = nullptr;   // column sums handed over by sk_hidden_error are for the very next call only
     if (target_rows > L->max_batch) return fail(c, SK_ERR_ALLOCATION_LIMIT, "target batches: received %u exceeds max %u", target_rows, L->max_batch);
     if (rows == 0 || rows > L->max_batch || rows > target_rows)
         return fail(c, SK_ERR_MISMATCHED_DIMENSIONS, "rows %u must be within target rows %u and max batch %u", rows, target_rows, L->max_batch);
@@ -771,6 +786,7 @@ int sk_backward_update(sk_ctx *c, const sk_dense *L, const void *x, uint32_t x_r
 int sk_ffn_forward(sk_ctx *c, const sk_dense *const *layers, uint32_t n, const void *x, uint32_t x_rows, uint32_t batch,
                    uint32_t use_dropout, uint32_t step, uint32_t row_offset) {
     if (!c || !layers) return SK_ERR_NULL_POINTER;
+    c->fused_colsum_key = nullptr;   // column sums handed over by sk_hidden_error are for the very next call only
     if (n == 0) return fail(c, SK_ERR_INVALID_CONFIGURATION, "Cannot execute a forward pass on an empty network");
     const void *cur = x;
     uint32_t rows = x_rows;
@@ -822,6 +838,7 @@ int sk_backward_grads(sk_ctx *c, const sk_dense *L, const void *x, uint32_t x_ro
     int rc = check_layer(c, L, true);
     if (rc) return rc;
     if (!x || !dw || !colsums) return fail(c, SK_ERR_NULL_POINTER, "input or output pointer is NULL");
+    c->fused_colsum_key = nullptr;   // column sums handed over by sk_hidden_error are for the very next call only
     if ((rc = check_batch(c, L, x_rows, batch))) return rc;
     return SK_DISPATCH(L->dtype, backward_grads_impl, c, L, x, batch, dw, colsums);
 }
@@ -831,6 +848,7 @@ int sk_apply_update(sk_ctx *c, const sk_dense *L, const float *dw, const float *
     int rc = check_layer(c, L, true);
     if (rc) return rc;
     if (!dw || !colsums || !lin || !nrm) return fail(c, SK_ERR_NULL_POINTER, "gradient or optimiser pointer is NULL");
+    c->fused_colsum_key = nullptr;   // column sums handed over by sk_hidden_error are for the very next call only
     if (batch_stat == 0) return fail(c, SK_ERR_INVALID_BATCH_SIZE, "Batch size must be more than zero.");
     if (lin->kind > 1 || nrm->kind > 1) return fail(c, SK_ERR_INVALID_CONFIGURATION, "optimiser ordinal out of range");
     return SK_DISPATCH(L->dtype, apply_update_impl, c, L, dw, colsums, batch_stat, lin, nrm, lr, clamp, step);
@@ -851,6 +869,7 @@ int sk_apply_update_rows(sk_ctx *c, const sk_dense *L, const void *grad, uint32_
     int rc = check_layer(c, L, true);
     if (rc) return rc;
     if (!grad || !lin) return fail(c, SK_ERR_NULL_POINTER, "gradient or optimiser pointer is NULL");
+    c->fused_colsum_key = nullptr;   // column sums handed over by sk_hidden_error are for the very next call only
     if (nrows == 0 || (uint64_t)row0 + nrows > L->K)
         return fail(c, SK_ERR_MISMATCHED_DIMENSIONS, "rows [%u, %u) outside the %u rows of the weight matrix", row0, row0 + nrows, L->K);
     if (lin->kind > 1) return fail(c, SK_ERR_INVALID_CONFIGURATION, "optimiser ordinal out of range");
@@ -862,6 +881,7 @@ int sk_apply_vector_update(sk_ctx *c, const sk_dense *L, const float *colsums, u
     int rc = check_layer(c, L, true);
     if (rc) return rc;
     if (!colsums || !lin || !nrm) return fail(c, SK_ERR_NULL_POINTER, "column sums or optimiser pointer is NULL");
+    c->fused_colsum_key = nullptr;   // column sums handed over by sk_hidden_error are for the very next call only
     if (batch_stat == 0) return fail(c, SK_ERR_INVALID_BATCH_SIZE, "Batch size must be more than zero.");
     if (lin->kind > 1 || nrm->kind > 1) return fail(c, SK_ERR_INVALID_CONFIGURATION, "optimiser ordinal out of range");
     return SK_DISPATCH(L->dtype, apply_vector_update_impl, c, L, colsums, batch_stat, lin, nrm, lr, clamp, step);
@@ -884,6 +904,7 @@ int sk_reduce_update_broadcast(sk_ctx *c, const sk_dense *L, void *const *peer_g
     int rc = check_layer(c, L, true);
     if (rc) return rc;
     if (!lin) return fail(c, SK_ERR_NULL_POINTER, "optimiser pointer is NULL");
+    c->fused_colsum_key = nullptr;   // column sums handed over by sk_hidden_error are for the very next call only
     if (lin->kind > 1) return fail(c, SK_ERR_INVALID_CONFIGURATION, "optimiser ordinal out of range");
     if ((rc = check_exchange(c, L, peer_grad, world, rank))) return rc;
     if ((rc = check_exchange(c, L, peer_w, world, rank))) return rc;
@@ -950,6 +971,7 @@ int sk_peer_free(sk_ctx *c, void *ptr) {
 
 int sk_copy(sk_ctx *c, void *dst, const void *src, size_t bytes) {
     if (!c || !dst || !src) return SK_ERR_NULL_POINTER;
+    c->fused_colsum_key = nullptr;   // column sums handed over by sk_hidden_error are for the very next call only
     return check_cuda(c, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, c->stream), "device copy");
 }
 
@@ -977,6 +999,7 @@ int sk_wait_flags(sk_ctx *c, const uint32_t *flags, uint32_t world, uint32_t val
 
 int sk_cast(sk_ctx *c, const void *src, uint32_t sd, void *dst, uint32_t dd, size_t len) {
     if (!c || !src || !dst) return SK_ERR_NULL_POINTER;
+    c->fused_colsum_key = nullptr;   // column sums handed over by sk_hidden_error are for the very next call only
     if (len == 0) return SK_OK;
     size_t blocks = (len + 1023) / 1024;
     const size_t cap = (size_t)c->num_sms * 16;
@@ -993,6 +1016,7 @@ int sk_cast(sk_ctx *c, const void *src, uint32_t sd, void *dst, uint32_t dd, siz
 
 int sk_fill(sk_ctx *c, void *dst, uint32_t dtype, float value, size_t len) {
     if (!c || !dst) return SK_ERR_NULL_POINTER;
+    c->fused_colsum_key = nullptr;   // column sums handed over by sk_hidden_error are for the very next call only
     if (len == 0) return SK_OK;
     size_t blocks = (len + 1023) / 1024;
     const size_t cap = (size_t)c->num_sms * 16;

@@ -71,6 +71,11 @@ class GpuContext:
         """Force the FFMA GEMM (True) or let the library pick the tensor-core kernel where it can (False)."""
         self._check(self.lib.sk_ctx_set_option(self.handle, 0, int(ffma_only)))
 
+    def set_colsum_handover(self, on: bool):
+        """Let gpu_hidden_layer_error hand the layer's column sums to the weight-gradient call that
+        follows it directly (the caller must not touch d_prenorm / d_norm_w / d_norm_b in between)."""
+        self._check(self.lib.sk_ctx_set_option(self.handle, 1, int(on)))
+
     def reserve(self, workspace_bytes: int):
         self._check(self.lib.sk_ctx_reserve(self.handle, workspace_bytes))
 

@@ -103,6 +103,9 @@ class DataParallelFFN:
         self.fused = scheme == "fused" or (scheme == "auto" and world > 1 and all(self.sharded) and world <= 8
                                             and hasattr(context, "signal_peers"))
         self.epoch = 0
+        if world > 1 and hasattr(context, "set_colsum_handover"):
+            # backward() calls the delta of a layer and its weight-gradient GEMM back to back
+            context.set_colsum_handover(True)
         if self.fused:
             self.dw, self.dw_shard = [], []      # the fused exchange stages gradients in its own arena
             self._map_peers(layers)
