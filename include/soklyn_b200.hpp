@@ -597,6 +597,27 @@ struct ParamState {
         }
         return s;
     }
+    // ParamState<f32>::cast_f16 (mlp.rs:203-220): 16-bit copies of w / b, the f32 values become the
+    // masters, the moments move over. Consumes the state.
+    ParamState cast_f16(const GpuContext &ctx, Precision p = Precision::FP16) && {
+        ParamState s;
+        s.w = w.clone(ctx).cast(ctx, p);
+        s.b = b.clone(ctx).cast(ctx, p);
+        s.master_w = std::make_unique<Tensor>(w.clone(ctx));
+        s.master_b = std::make_unique<Tensor>(b.clone(ctx));
+        s.dv_w = std::move(dv_w); s.dv_b = std::move(dv_b); s.dm_w = std::move(dm_w); s.dm_b = std::move(dm_b);
+        ctx.synchronize(); // the temporaries of clone().cast() are released here
+        return s;
+    }
+    // ParamState<f16>::cast_f32 (mlp.rs:185-200): the masters become w / b.
+    ParamState cast_f32(const GpuContext &ctx) && {
+        if (!master_w || !master_b) throw InvalidConfiguration("16-bit parameter state without f32 masters");
+        ParamState s;
+        s.w = master_w->clone(ctx);
+        s.b = master_b->clone(ctx);
+        s.dv_w = std::move(dv_w); s.dv_b = std::move(dv_b); s.dm_w = std::move(dm_w); s.dm_b = std::move(dm_b);
+        return s;
+    }
     // mlp.rs:112-160: the optional tensors must have the shape of w / b
     void validate() const {
         auto same = [](const char *name, const std::unique_ptr<Tensor> &t, const Tensor &ref) {
@@ -673,6 +694,21 @@ class DenseBlock {
     Regularisation get_regularisation() const { return cfg_.regularisation; }
     bool is_training_mode() const { return is_training_; }
     Precision precision() const { return precision_; }
+
+    // DenseBlock<f32>::convert_f16 (mlp.rs:835-858) and DenseBlock<f16>::convert_f32 (mlp.rs:861-888):
+    // parameters through the ParamState casts, forward cache and mask through a device cast, the
+    // f32 gradient tensors move over. Both consume the block: call as std::move(block).convert_f16(ctx).
+    DenseBlock convert_f16(const GpuContext &ctx, Precision p = Precision::FP16) && {
+        if (precision_ != Precision::FP32 || p == Precision::FP32)
+            throw UnsupportedTypeCast(precision_name(precision_), precision_name(p));
+        ParamState lin = std::move(linear_).cast_f16(ctx, p), nrm = std::move(norm_).cast_f16(ctx, p);
+        return std::move(*this).converted(ctx, std::move(lin), std::move(nrm), p);
+    }
+    DenseBlock convert_f32(const GpuContext &ctx) && {
+        if (precision_ == Precision::FP32) throw UnsupportedTypeCast(precision_name(precision_), "FP32");
+        ParamState lin = std::move(linear_).cast_f32(ctx), nrm = std::move(norm_).cast_f32(ctx);
+        return std::move(*this).converted(ctx, std::move(lin), std::move(nrm), Precision::FP32);
+    }
 
     void set_mask_coeff(float v) { cfg_.mask_coeff = v; refresh(); }
     void set_normalisation(Normalisation v) { cfg_.normalisation = v; refresh(); }
@@ -777,6 +813,22 @@ class DenseBlock {
         if (is_training && p != Precision::FP32)
             d_prenorm_lp_ = std::make_unique<Tensor>(Tensor::zeros(ctx, max_batch, wc, p, false));
         refresh();
+    }
+    DenseBlock converted(const GpuContext &ctx, ParamState lin, ParamState nrm, Precision p) && {
+        DenseBlock b;
+        b.precision_ = p; b.is_training_ = is_training_; b.max_batch_ = max_batch_; b.cfg_ = cfg_;
+        b.linear_ = std::move(lin);
+        b.norm_ = std::move(nrm);
+        b.out_ = out_.cast(ctx, p); b.predrop_ = predrop_.cast(ctx, p); b.preact_ = preact_.cast(ctx, p);
+        b.centered_ = centered_.cast(ctx, p); b.prenorm_ = prenorm_.cast(ctx, p); b.norm_rstd_ = norm_rstd_.cast(ctx, p);
+        b.grad_ = std::move(grad_); b.d_prenorm_ = std::move(d_prenorm_);
+        b.d_norm_w_ = std::move(d_norm_w_); b.d_norm_b_ = std::move(d_norm_b_);
+        b.mask_ = mask_.cast(ctx, p);
+        if (is_training_ && p != Precision::FP32)
+            b.d_prenorm_lp_ = std::make_unique<Tensor>(Tensor::zeros(ctx, max_batch_, b.out_.cols(), p, false));
+        b.refresh();
+        ctx.synchronize(); // the casts read this block's tensors, which go away with it
+        return b;
     }
     void refresh() {
         auto f = [](const std::unique_ptr<Tensor> &t) { return t ? (float *)t->ptr() : nullptr; };

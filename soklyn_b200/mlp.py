@@ -44,6 +44,17 @@ class ParamState:
         master_b = Tensor.zeros(context, shape) if half else None
         return ParamState(w, b, master_w, master_b, delta(), delta(), delta(), delta())
 
+    def cast_f16(self, context, precision=Precision.FP16):
+        """ParamState<f32>::cast_f16 (src/mlp.rs:203-220): 16-bit copies of w / b, the f32 values
+        become the masters, the moments move over."""
+        return ParamState(self.w.clone(context).cast(context, precision), self.b.clone(context).cast(context, precision),
+                          self.w.clone(context), self.b.clone(context), self.dv_w, self.dv_b, self.dm_w, self.dm_b)
+
+    def cast_f32(self, context):
+        """ParamState<f16>::cast_f32 (src/mlp.rs:185-200): the masters become w / b."""
+        return ParamState(self.master_w.clone(context), self.master_b.clone(context), None, None,
+                          self.dv_w, self.dv_b, self.dm_w, self.dm_b)
+
     def validate(self):
         """src/mlp.rs:112-160: shapes of the optional tensors must match w / b."""
         for name, ref in (("master_w", self.w), ("dv_w", self.w), ("dm_w", self.w),
@@ -140,6 +151,42 @@ class DenseBlock:
     def set_normalisation(self, v): self.normalisation = v; self._desc = None
     def set_activation(self, v): self.activation = v; self._desc = None
     def set_regularisation(self, v): self.regularisation = v; self._desc = None
+
+    def _converted(self, context, linear, norm, precision):
+        """Shared body of convert_f16 / convert_f32 (src/mlp.rs:835-888): parameters through the
+        ParamState casts, the six forward-cache tensors and the mask through a device cast, the
+        f32 gradient tensors move over unchanged. The source block must not be used afterwards."""
+        if (precision == Precision.FP32) == (self.precision == Precision.FP32):
+            raise log.UnsupportedTypeCast(self.precision, precision)
+        blk = DenseBlock.__new__(DenseBlock)
+        blk.precision, blk.linear_state, blk.norm_state = precision, linear, norm
+        c = lambda t: t.cast(context, precision)
+        blk.out, blk.predrop_out, blk.preact_out = c(self.out), c(self.predrop_out), c(self.preact_out)
+        blk.centered_out, blk.prenorm_out, blk.norm_rstd = c(self.centered_out), c(self.prenorm_out), c(self.norm_rstd)
+        blk.grad, blk.d_prenorm_out, blk.d_norm_w, blk.d_norm_b = self.grad, self.d_prenorm_out, self.d_norm_w, self.d_norm_b
+        blk.mask = c(self.mask)
+        blk.d_prenorm_lp = (Tensor.zeros(context, tuple(self.out.data.shape), precision, take_id=False)
+                            if self.is_training and precision != Precision.FP32 else None)
+        blk.max_batch_size = self.max_batch_size
+        blk.normalisation, blk.activation = self.normalisation, self.activation
+        blk.regularisation, blk.mask_coeff = self.regularisation, self.mask_coeff
+        blk.is_training = self.is_training
+        blk._desc = None
+        return blk
+
+    def convert_f16(self, context, precision: Precision = Precision.FP16) -> "DenseBlock":
+        """DenseBlock<f32>::convert_f16 (src/mlp.rs:835-858); `precision` may also name BF16."""
+        if self.precision != Precision.FP32:
+            raise log.UnsupportedTypeCast(self.precision, precision)
+        return self._converted(context, self.linear_state.cast_f16(context, precision),
+                               self.norm_state.cast_f16(context, precision), precision)
+
+    def convert_f32(self, context) -> "DenseBlock":
+        """DenseBlock<f16>::convert_f32 (src/mlp.rs:861-888)."""
+        if self.precision == Precision.FP32:
+            raise log.UnsupportedTypeCast(self.precision, Precision.FP32)
+        return self._converted(context, self.linear_state.cast_f32(context), self.norm_state.cast_f32(context),
+                               Precision.FP32)
 
     def reset_mask(self, context):
         self.mask.broadcast(context, 1.0)

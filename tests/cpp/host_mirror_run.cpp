@@ -180,6 +180,20 @@ int device_checks(const GpuContext &ctx) {
         Tensor hx = Tensor::zeros(odd, 4, 8, Precision::FP16);
         ok += expect_throw<HardwareConstraintViolation>("tile dim", [&] { hb.forward(odd, hx, 4, false, 1); });
     }
+    {   // convert_f16 / convert_f32 (src/mlp.rs:835-888): the f32 parameters survive the round trip bit for bit
+        InitXavierUniformFunc init(5);
+        DenseBlock f(ctx, true, 8, 16, 4, init);
+        const std::vector<float> w0 = f.get_weights().download(ctx);
+        DenseBlock h = std::move(f).convert_f16(ctx);
+        bool good = h.precision() == Precision::FP16 && h.get_master_weights() && h.get_master_weights()->download(ctx) == w0 &&
+                    h.get_weights().precision() == Precision::FP16 && h.get_grads() && h.desc().d_prenorm_lp;
+        Tensor hx = Tensor::zeros(ctx, 4, 8, Precision::FP16);
+        h.forward(ctx, hx, 4, false, 1);
+        ok += expect_throw<UnsupportedTypeCast>("f16 -> f16", [&] { DenseBlock again = std::move(h).convert_f16(ctx); });
+        DenseBlock back = std::move(h).convert_f32(ctx);
+        good = good && back.precision() == Precision::FP32 && !back.get_master_weights() && back.get_weights().download(ctx) == w0;
+        ok += good ? 1 : -1000;
+    }
     std::vector<DenseBlock> layers;
     layers.push_back(std::move(a));
     layers.push_back(std::move(b));
@@ -189,8 +203,8 @@ int device_checks(const GpuContext &ctx) {
     Tensor t8 = Tensor::zeros(ctx, 4, 8);
     ok += expect_throw<InvalidConfiguration>("optimiser count", [&] { net.backward(ctx, outs, t8, x, LossConfig{}, one, 1); });
     ctx.synchronize();
-    if (ok != 14) std::fprintf(stderr, "%d of 14 device checks passed\n", ok);
-    return ok == 14 ? 0 : 1;
+    if (ok != 16) std::fprintf(stderr, "%d of 16 device checks passed\n", ok);
+    return ok == 16 ? 0 : 1;
 }
 
 int train(const char *in_path, const char *out_path) {

@@ -250,3 +250,52 @@ def test_regularisation_and_nesterov_momentum_match_oracle(gpu_ctx, regu, nester
                       ("norm_w", blk.get_norm_weights()), ("norm_b", blk.get_norm_biases())):
         e = H.relerr(got.download(gpu_ctx).reshape(-1), getattr(oblk, name).reshape(-1))
         assert e <= 2e-5, f"{name}: {e:.2e}"
+
+
+def test_convert_f16_and_back(gpu_ctx):
+    """DenseBlock::convert_f16 / convert_f32 (src/mlp.rs:835-888): the f32 parameters become the masters
+    bit for bit, the 16-bit copies are their roundings, moments and gradient tensors move over, training
+    continues within the 16-bit tolerance of an f32 network that was never converted, and converting
+    back returns the masters."""
+    from soklyn_b200.core import Tensor
+    from soklyn_b200.ffn import FeedForwardNetwork
+    from soklyn_b200.function import Precision
+    spec = configs.scaled(configs.CONFIGS[2], dims=(96, 64, 32, 96), batch=48, precision="f32", name="convert")
+    w = configs.make_weights(spec)
+    x, t, _ = configs.make_data(spec)
+    ref_net, _ = H.run_device(gpu_ctx, spec, w, x, t, 3)          # three f32 steps, never converted
+    net, _ = H.run_device(gpu_ctx, spec, w, x, t, 2)              # two f32 steps, then convert
+    before = [{k: getattr(l, g)().download(gpu_ctx) for k, g in
+               (("w", "get_weights"), ("b", "get_biases"), ("dm", "get_dm_weights"), ("out", "get_outputs"))}
+              for l in net.get_layers()]
+    moments = [l.get_dm_weights() for l in net.get_layers()]
+    half = [l.convert_f16(gpu_ctx) for l in net.get_layers()]
+    for blk, old, dm in zip(half, before, moments):
+        assert blk.precision == Precision.FP16 and blk.get_dm_weights() is dm
+        assert np.array_equal(blk.get_master_weights().download(gpu_ctx), old["w"])
+        assert np.array_equal(blk.get_master_biases().download(gpu_ctx), old["b"])
+        assert np.array_equal(blk.get_weights().download(gpu_ctx), old["w"].astype(np.float16))
+        assert np.array_equal(blk.get_outputs().download(gpu_ctx), old["out"].astype(np.float16))
+        assert np.array_equal(blk.get_masks().download(gpu_ctx), np.ones_like(old["out"], np.float16))
+        with pytest.raises(log.UnsupportedTypeCast):
+            blk.convert_f16(gpu_ctx)
+    hnet = FeedForwardNetwork(half, spec.dims[0])
+    xd = Tensor.from_cpu_vector(gpu_ctx, x, x.shape, Precision.FP16)
+    td = Tensor.from_cpu_vector(gpu_ctx, t, t.shape, Precision.FP16)
+    outs = hnet.forward(gpu_ctx, xd, spec.batch, False, 3)
+    hnet.backward(gpu_ctx, outs, td, xd, spec.loss_config(), spec.train_context(), 3)
+    gpu_ctx.synchronize()
+    for blk, ref in zip(half, ref_net.get_layers()):
+        assert H.relerr(blk.get_outputs().download(gpu_ctx), ref.get_outputs().download(gpu_ctx)) <= 1e-2
+        diff = np.abs(blk.get_master_weights().download(gpu_ctx) - ref.get_weights().download(gpu_ctx))
+        assert diff.max() <= 2.5 * spec.lr and (diff > 0.1 * spec.lr).mean() <= 0.01
+    masters = [l.get_master_weights().download(gpu_ctx) for l in half]
+    back = [l.convert_f32(gpu_ctx) for l in half]
+    for blk, m in zip(back, masters):
+        assert blk.precision == Precision.FP32 and blk.get_master_weights() is None
+        assert np.array_equal(blk.get_weights().download(gpu_ctx), m)
+        with pytest.raises(log.UnsupportedTypeCast):
+            blk.convert_f32(gpu_ctx)
+    fnet = FeedForwardNetwork(back, spec.dims[0])
+    xf = Tensor.from_cpu_vector(gpu_ctx, x, x.shape)
+    assert np.isfinite(fnet.forward(gpu_ctx, xf, spec.batch, False, 4)[-1].download(gpu_ctx)).all()
