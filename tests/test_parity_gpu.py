@@ -133,3 +133,61 @@ def test_tensor_core_gemm_matches_ffma_gemm(gpu_ctx, spec):
                 tol = 4e-3 if spec.precision == "f16" else 1.6e-2   # a couple of ulps of the storage type
                 assert e <= tol, f"layer {i} {name}: tensor-core vs FFMA relative error {e:.3e}"
         assert np.array_equal(a["mask"], b["mask"])
+
+
+def test_two_heads_on_one_trunk_match_oracle(gpu_ctx):
+    """The reference's multi-head pattern (examples/cifar_ten_train.rs:175-244): two output blocks read the
+    same trunk output, each step trains one of them and back-propagates it into the trunk through the
+    per-block calls, the second head with its own learning rate and a gradient clamp."""
+    import soklyn_b200 as sk
+    from soklyn_b200.core import Tensor, reset_tensor_ids
+    from soklyn_b200.context import LayerInitConfig, LossConfig, TrainContext
+    from soklyn_b200.function import Activation, LossFunc, Normalisation, Optimiser, Regularisation
+    batch, dims, heads = 40, (72, 64, 48), (10, 2)
+    rng = np.random.Generator(np.random.PCG64(77))
+    ws = [rng.standard_normal((dims[i], dims[i + 1]), dtype=np.float32) * np.float32(np.sqrt(2.0 / dims[i])) for i in range(2)]
+    ws += [rng.standard_normal((dims[2], h), dtype=np.float32) * np.float32(np.sqrt(2.0 / dims[2])) for h in heads]
+    x = rng.standard_normal((batch, dims[0]), dtype=np.float32)
+    labels = [rng.integers(0, h, batch) for h in heads]
+    targets = [np.eye(h, dtype=np.float32)[l] for h, l in zip(heads, labels)]
+
+    reset_tensor_ids(0)
+    cfgs = [LayerInitConfig(Normalisation.LayerNorm, Activation.Mish, Regularisation.none(), 0.2)] * 2 + [LayerInitConfig()] * 2
+    shapes = [(dims[0], dims[1]), (dims[1], dims[2]), (dims[2], heads[0]), (dims[2], heads[1])]
+    dev = [sk.DenseBlock(gpu_ctx, True, k, n, batch, configs._GivenWeights(w), c) for (k, n), w, c in zip(shapes, ws, cfgs)]
+    ora = [ok.OracleBlock(w, batch, norm="layer" if i < 2 else "disabled", act="mish" if i < 2 else "identity",
+                          mask_coeff=0.2 if i < 2 else 0.0, tensor_id=dev[i].get_weights().get_id()) for i, w in enumerate(ws)]
+    xd = Tensor.from_cpu_vector(gpu_ctx, x, x.shape)
+    td = [Tensor.from_cpu_vector(gpu_ctx, t, t.shape) for t in targets]
+    loss = LossConfig(LossFunc.CrossEntropyLoss, Activation.Softmax)
+    for step in range(1, 5):
+        head = 0 if step % 2 else 1
+        lr, clamp = (1e-3, 0.05) if head == 0 else (1e-5, 1e-6)
+        # device: forward through the trunk and both heads, then the chosen head backwards
+        o0 = dev[0].forward(gpu_ctx, xd, batch, True, step)
+        o1 = dev[1].forward(gpu_ctx, o0, batch, True, step)
+        for h in (2, 3):
+            dev[h].forward(gpu_ctx, o1, batch, True, step)
+        tc = TrainContext(Optimiser.Adam(), Optimiser.Adam(), batch, lr, clamp)
+        dev[2 + head].compute_loss(gpu_ctx, td[head], loss)
+        dev[2 + head].backward_output(gpu_ctx, o1, tc, step)
+        dev[1].backward_hidden(gpu_ctx, dev[2 + head], o0, tc, step)
+        dev[0].backward_hidden(gpu_ctx, dev[1], xd, tc, step)
+        # oracle: the same calls
+        p0 = ora[0].forward(x, batch, True, step)
+        p1 = ora[1].forward(p0, batch, True, step)
+        for h in (2, 3):
+            ora[h].forward(p1, batch, True, step)
+        oc = ok.TrainContext(ok.adam(), ok.adam(), batch, lr, clamp)
+        ora[2 + head].compute_loss(targets[head], "ce", "softmax")
+        ora[2 + head].backward_output(p1, oc, step)
+        ora[1].backward_hidden(ora[2 + head], p0, oc, step)
+        ora[0].backward_hidden(ora[1], x, oc, step)
+    gpu_ctx.synchronize()
+    for i, (d, o) in enumerate(zip(dev, ora)):
+        got, ref = H.device_state(gpu_ctx, d), o.state()
+        assert np.array_equal(got["mask"], ref["mask"]), f"block {i} mask"
+        for name in ("out", "preact", "grad", "d_prenorm", "dm_w", "dm_nw"):
+            assert H.relerr(got[name].reshape(ref[name].shape), ref[name]) <= 5e-4, f"block {i} {name}"
+        for name in ("w", "b", "norm_w", "norm_b"):   # Adam: distance from the oracle in units of the largest rate
+            assert np.abs(got[name].reshape(ref[name].shape) - ref[name]).max() <= 0.1 * 1e-3 * 4, f"block {i} {name}"
