@@ -136,6 +136,18 @@ uint32_t sk_scramble_seed(uint32_t step, uint32_t tensor_id);
 int sk_dense_forward(sk_ctx *ctx, const sk_dense *layer, const void *x, uint32_t x_rows,
                      uint32_t batch, uint32_t use_dropout, uint32_t step, uint32_t row_offset);
 
+/* BatchNorm forward for a batch whose rows are split over several devices (no counterpart: the
+ * reference is single-device; arithmetic of src/cuda/kernel/forward.cu's BatchNorm branch with the
+ * column statistics taken over all batch_stat rows). stats is device f32 [2 x N]. Three calls with
+ * the same arguments, the caller summing over ranks in between:
+ *   phase 0: GEMM into prenorm; stats[0][col] = this shard's sum of x          -> sum stats[0] over ranks
+ *   phase 1: stats[1][col] = this shard's sum of (x - mean)^2                  -> sum stats[1] over ranks
+ *   phase 2: centered, rstd, preact, activation and dropout from the summed statistics.
+ * The backward entry points already take batch_stat for BatchNorm's 1/M. */
+int sk_dense_forward_batchnorm(sk_ctx *ctx, const sk_dense *layer, const void *x, uint32_t x_rows, uint32_t batch,
+                               uint32_t batch_stat, uint32_t phase, float *stats, uint32_t use_dropout,
+                               uint32_t step, uint32_t row_offset);
+
 /* GpuContext::gpu_compute_output_layer_error (src/io/device/ffn_device.rs:141-231) with the
  * checks of DenseBlock::compute_loss (src/mlp.rs:756-821). Works on `rows` rows of the block's
  * `out` (the reference always passes out.rows() == max_batch); target is T [>= rows x N].

@@ -103,6 +103,8 @@ _SIGS = {
     "sk_scramble_seed": (C.c_uint32, [C.c_uint32, C.c_uint32]),
     "sk_dense_forward": (C.c_int, [C.c_void_p, C.POINTER(SkDense), C.c_void_p, C.c_uint32, C.c_uint32,
                                    C.c_uint32, C.c_uint32, C.c_uint32]),
+    "sk_dense_forward_batchnorm": (C.c_int, [C.c_void_p, C.POINTER(SkDense), C.c_void_p, C.c_uint32, C.c_uint32,
+                                             C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32]),
     "sk_output_error": (C.c_int, [C.c_void_p, C.POINTER(SkDense), C.c_void_p, C.c_uint32, C.c_uint32,
                                   C.c_uint32, C.c_uint32, C.c_float]),
     "sk_hidden_error": (C.c_int, [C.c_void_p, C.POINTER(SkDense), C.POINTER(SkDense), C.c_uint32, C.c_uint32]),

@@ -227,7 +227,7 @@ bool layer_vec_ok(const sk_dense *L) {
 // ------------------------------------------------------------------------------------------
 template <typename T>
 int forward_impl(sk_ctx *c, const sk_dense *L, const void *x, uint32_t batch, uint32_t use_dropout, uint32_t step,
-                 uint32_t row_offset) {
+                 uint32_t row_offset, bool gemm_only = false) {
     const uint32_t seed = sk_scramble_seed(step, L->tensor_id);
     const bool has_norm = L->norm != SK_NORM_DISABLED;
     const bool vec = layer_vec_ok(L);
@@ -244,7 +244,7 @@ int forward_impl(sk_ctx *c, const sk_dense *L, const void *x, uint32_t batch, ui
                                                                L->N, batch, L->N, L->K, epi), "forward gemm");
     }
     c->launches++;
-    if (rc || !has_norm) return rc;
+    if (rc || !has_norm || gemm_only) return rc;
     ProfScope ps(c, SK_PROF_NORM);
     ActDrop ad{L->act, use_dropout, seed, row_offset, L->leaky_coeff, L->mask_coeff};
     if (L->norm == SK_NORM_BATCH) {
@@ -263,6 +263,23 @@ int forward_impl(sk_ctx *c, const sk_dense *L, const void *x, uint32_t batch, ui
     }
     c->launches++;
     return check_cuda(c, cudaGetLastError(), "forward norm");
+}
+
+// BatchNorm forward in phases for a batch that is split over devices (see norm_cols_phase_kernel).
+template <typename T>
+int forward_batchnorm_impl(sk_ctx *c, const sk_dense *L, const void *x, uint32_t batch, uint32_t batch_stat, uint32_t phase,
+                           float *stats, uint32_t use_dropout, uint32_t step, uint32_t row_offset) {
+    if (phase == 0) {
+        const int rc = forward_impl<T>(c, L, x, batch, use_dropout, step, row_offset, true);
+        if (rc) return rc;
+    }
+    ProfScope ps(c, SK_PROF_NORM);
+    ActDrop ad{L->act, use_dropout, sk_scramble_seed(step, L->tensor_id), row_offset, L->leaky_coeff, L->mask_coeff};
+    norm_cols_phase_kernel<T><<<(L->N + 31) / 32, kRowThreads, 0, c->stream>>>(
+        phase, stats, batch_stat, (const T *)L->prenorm, (const T *)L->norm_w, (const T *)L->norm_b, (T *)L->centered,
+        (T *)L->preact, (T *)L->predrop, (T *)L->out, (T *)L->mask, (T *)L->norm_rstd, batch, L->N, ad);
+    c->launches++;
+    return check_cuda(c, cudaGetLastError(), "forward batch norm phase");
 }
 
 template <typename T>
@@ -736,6 +753,21 @@ int sk_dense_forward(sk_ctx *c, const sk_dense *L, const void *x, uint32_t x_row
     c->fused_colsum_key = nullptr;   // column sums handed over by sk_hidden_error are for the very next call only
     if ((rc = check_batch(c, L, x_rows, batch))) return rc;
     return SK_DISPATCH(L->dtype, forward_impl, c, L, x, batch, use_dropout, step, row_offset);
+}
+
+int sk_dense_forward_batchnorm(sk_ctx *c, const sk_dense *L, const void *x, uint32_t x_rows, uint32_t batch,
+                               uint32_t batch_stat, uint32_t phase, float *stats, uint32_t use_dropout, uint32_t step,
+                               uint32_t row_offset) {
+    int rc = check_layer(c, L, false);
+    if (rc) return rc;
+    if (!x || !stats) return fail(c, SK_ERR_NULL_POINTER, "input or statistics pointer is NULL");
+    c->fused_colsum_key = nullptr;
+    if (L->norm != SK_NORM_BATCH) return fail(c, SK_ERR_INVALID_CONFIGURATION, "the block's normalisation is not BatchNorm");
+    if (phase > 2) return fail(c, SK_ERR_INVALID_CONFIGURATION, "BatchNorm phase %u (0, 1 or 2)", phase);
+    if (batch_stat < batch || batch_stat < 2)
+        return fail(c, SK_ERR_INVALID_BATCH_SIZE, "BatchNorm statistics over %u rows with %u local rows", batch_stat, batch);
+    if ((rc = check_batch(c, L, x_rows, batch))) return rc;
+    return SK_DISPATCH(L->dtype, forward_batchnorm_impl, c, L, x, batch, batch_stat, phase, stats, use_dropout, step, row_offset);
 }
 
 int sk_output_error(sk_ctx *c, const sk_dense *L, const void *target, uint32_t target_rows, uint32_t rows,

@@ -191,6 +191,59 @@ norm_cols_kernel(const T *__restrict__ prenorm, const T *__restrict__ norm_w, co
     }
 }
 
+// BatchNorm with the batch split over several devices, in three phases around two sums over
+// ranks (stats is f32 [2 x N]): phase 0 writes this shard's column sums of prenorm to stats[0];
+// phase 1 takes the summed stats[0] and writes this shard's sums of (x - mean)^2 to stats[1];
+// phase 2 takes both summed rows and does what norm_cols_kernel does after its reductions.
+// m_stat is the whole batch. Same thread layout as norm_cols_kernel.
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+norm_cols_phase_kernel(uint32_t phase, float *__restrict__ stats, uint32_t m_stat, const T *__restrict__ prenorm,
+                       const T *__restrict__ norm_w, const T *__restrict__ norm_b, T *__restrict__ centered,
+                       T *__restrict__ preact, T *__restrict__ predrop, T *__restrict__ out, T *__restrict__ mask,
+                       T *__restrict__ rstd_out, uint32_t M, uint32_t N, ActDrop ad) {
+    __shared__ float red[8][33];
+    const uint32_t cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+    const uint32_t col = blockIdx.x * 32 + cx;
+    const bool live = col < N;
+    auto reduce = [&](float v) {
+        red[ry][cx] = v;
+        __syncthreads();
+        float t = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) t += red[i][cx];
+        __syncthreads();
+        return t;
+    };
+    if (phase == 0) {
+        float s = 0.0f;
+        if (live) for (uint32_t r = ry; r < M; r += 8) s += to_f32(prenorm[(size_t)r * N + col]);
+        s = reduce(s);
+        if (live && ry == 0) stats[col] = s;
+        return;
+    }
+    const float mean = live ? stats[col] / (float)m_stat : 0.0f;
+    if (phase == 1) {
+        float q = 0.0f;
+        if (live) for (uint32_t r = ry; r < M; r += 8) { const float d = to_f32(prenorm[(size_t)r * N + col]) - mean; q += d * d; }
+        q = reduce(q);
+        if (live && ry == 0) stats[N + col] = q;
+        return;
+    }
+    if (!live) return;
+    const float rstd = rsqrtf(stats[N + col] / (float)m_stat + 1e-6f);
+    if (ry == 0) rstd_out[col] = from_f32<T>(rstd);
+    const float nw = to_f32(norm_w[col]), nb = to_f32(norm_b[col]);
+    for (uint32_t r = ry; r < M; r += 8) {
+        const size_t idx = (size_t)r * N + col;
+        const float d = to_f32(prenorm[idx]) - mean;
+        centered[idx] = from_f32<T>(d);
+        float pre[1] = {round_to<T>(d * rstd * nw + nb)};
+        preact[idx] = from_f32<T>(pre[0]);
+        act_drop_store<T, 1>(ad, pre, r, col, idx, predrop, out, mask, false, 1);
+    }
+}
+
 // Output-layer delta, one warp per row: optional in-place softmax of `out`
 // (util.cu:95-173), then delta and the normalisation backward with loss scale 512
 // (ffn/backward.cu:12-56). Also writes the 16-bit copy of d_prenorm when given.

@@ -129,6 +129,15 @@ class GpuContext:
         self._check(self.lib.sk_dense_forward(self.handle, C.byref(layer.desc()), input.ptr(), input.rows(),
                                               batch_size, int(use_dropout), step & 0xFFFFFFFF, row_offset))
 
+    def gpu_forward_batchnorm_phase(self, layer, input: Tensor, batch_size: int, batch_stat: int, phase: int,
+                                    stats: torch.Tensor, use_dropout: bool, step: int, row_offset: int = 0):
+        """One of the three phases of a BatchNorm forward whose batch is split over ranks; `stats` is an
+        f32 [2 x N] device tensor the caller sums over ranks between the phases."""
+        self.check_tile_dim(layer.precision)
+        self._check(self.lib.sk_dense_forward_batchnorm(self.handle, C.byref(layer.desc()), input.ptr(), input.rows(),
+                                                        batch_size, batch_stat, phase, stats.data_ptr(),
+                                                        int(use_dropout), step & 0xFFFFFFFF, row_offset))
+
     def gpu_compute_output_layer_error(self, layer, target: Tensor, err_mode: LossFunc, activation: Activation):
         rows = layer.get_outputs().rows()
         self._check(self.lib.sk_output_error(self.handle, C.byref(layer.desc()), target.ptr(), target.rows(), rows,

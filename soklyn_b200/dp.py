@@ -28,7 +28,8 @@ Two exchange schemes:
   All flag waits are bounded (SK_ERR_DEVICE_TIMEOUT instead of a hang). Only the small column sums
   still use an NCCL all-reduce.
 
-BatchNorm layers would need their column statistics all-reduced as well; that is not built.
+BatchNorm blocks (hidden ones) run their forward in three phases around two all-reduces of the column
+statistics, so that mean and variance are those of the whole batch.
 """
 from __future__ import annotations
 
@@ -76,9 +77,15 @@ class DataParallelFFN:
         self.ctx, self.net, self.group = context, network, group
         self.rank, self.world, self.global_batch = rank, world, global_batch
         self.row_offset, self.local_batch = shard_rows(global_batch, rank, world)
-        for layer in network.get_layers():
-            if layer.get_normalisation() == Normalisation.BatchNorm and world > 1:
-                raise log.InvalidConfiguration("BatchNorm is not supported under data parallelism")
+        # BatchNorm takes its column statistics over the whole batch: its forward runs in three phases
+        # with two small all-reduces (hidden blocks only: the output-layer delta has no global 1/M).
+        self.bn_stats = {}
+        if world > 1:
+            for i, layer in enumerate(network.get_layers()):
+                if layer.get_normalisation() == Normalisation.BatchNorm:
+                    if i == len(network.get_layers()) - 1:
+                        raise log.InvalidConfiguration("BatchNorm on the output block is not supported under data parallelism")
+                    self.bn_stats[i] = torch.zeros(2, layer.get_weights().cols(), device=context.device, dtype=torch.float32)
         dev = context.device
         layers = network.get_layers() if world > 1 else []
         self.fused = False
@@ -178,7 +185,24 @@ class DataParallelFFN:
         return 0, k
 
     def forward(self, input: Tensor, use_dropout: bool, step: int):
-        return self.net.forward(self.ctx, input, self.local_batch, use_dropout, step, self.row_offset)
+        if not self.bn_stats:
+            return self.net.forward(self.ctx, input, self.local_batch, use_dropout, step, self.row_offset)
+        outputs, cur = [], input
+        for i, layer in enumerate(self.net.get_layers()):
+            stats = self.bn_stats.get(i)
+            if stats is None:
+                cur = layer.forward(self.ctx, cur, self.local_batch, use_dropout, step, self.row_offset)
+            else:
+                layer.check_input_dimension(cur, self.local_batch)
+                for phase in (0, 1, 2):
+                    self.ctx.gpu_forward_batchnorm_phase(layer, cur, self.local_batch, self.global_batch, phase, stats,
+                                                         use_dropout, step, self.row_offset)
+                    if phase < 2:
+                        dist.all_reduce(stats[phase], group=self.group)
+                        self.collectives += 1
+                cur = layer.get_outputs()
+            outputs.append(cur)
+        return outputs
 
     def _exchange(self, i: int):
         if self.world > 1:

@@ -32,7 +32,14 @@ def main():
     specs = [(configs.scaled(configs.CONFIGS[4], dims=(256, 512, 256, 512, 256), batch=256, name="dp_fused_f16"), "fused"),
              (configs.scaled(configs.CONFIGS[4], dims=(256, 512, 256, 512, 256), batch=256, name="dp_sharded_f16"), "sharded"),
              (configs.scaled(configs.CONFIGS[3], dims=(384, 256, 128, 16), batch=128, name="dp_dropout_layernorm_f16"), "auto"),
-             (configs.scaled(configs.CONFIGS[1], dims=(96, 64, 32, 10), batch=64, name="dp_allreduce_f32"), "auto")]
+             (configs.scaled(configs.CONFIGS[1], dims=(96, 64, 32, 10), batch=64, name="dp_allreduce_f32"), "auto"),
+             # BatchNorm: column statistics over the whole batch through the three-phase forward
+             (configs.NetSpec(8, "dp_batchnorm_f32", (80, 64, 48, 12), ("batch", "batch", "disabled"),
+                              ("tanh", "silu", "identity"), (0.0, 0.1, 0.0), "f32", "mse", "identity", "sgd", 0.05, 64,
+                              "he_normal", "normal", "normal", True), "auto"),
+             (configs.NetSpec(8, "dp_batchnorm_f16", (128, 256, 128, 16), ("batch", "rms", "disabled"),
+                              ("silu", "silu", "identity"), (0.0, 0.0, 0.0), "f16", "mse", "identity", "adam", 1e-3, 128,
+                              "xavier_normal", "normal", "normal"), "auto")]
     ok = True
     for spec, scheme in specs:
         w = configs.make_weights(spec)

@@ -121,3 +121,67 @@ def test_shard_rows_and_single_rank_path():
     assert shard_rows(10, 0, 1) == (0, 10)
     with pytest.raises(sklog.InvalidBatchSize):
         shard_rows(10, 0, 4)
+
+
+def _bn_worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from soklyn_b200.dp import DataParallelFFN
+    from soklyn_b200.ffn import FeedForwardNetwork
+    from soklyn_b200.function import Normalisation
+    log = []
+
+    class BnLayer(_Layer):
+        def check_input_dimension(self, x, batch):
+            log.append(("check", self.idx, x.rows(), batch))
+
+        def get_outputs(self):
+            return _T(4, self.n)
+
+    class BnCtx(_Ctx):
+        def gpu_forward_batchnorm_phase(self, layer, x, batch, batch_stat, phase, stats, use_dropout, step, row_offset=0):
+            if phase < 2:
+                stats[phase].fill_(float((self.rank + 1) * (phase + 1)))     # this shard's partial sums
+            log.append(("bn", layer.idx, phase, batch, batch_stat, row_offset, stats.clone().tolist()))
+
+    layers = [BnLayer(6, 5, 0, log), _Layer(5, 3, 1, log)]
+    layers[0].norm = Normalisation.BatchNorm
+    dp = DataParallelFFN(BnCtx(rank, log), FeedForwardNetwork(layers, 6), global_batch=8, rank=rank, world=world)
+    outs = dp.forward(_T(4, 6), True, 3)
+    q.put((rank, log, len(outs), dp.collectives))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_batchnorm_forward_sums_statistics_over_ranks_between_phases():
+    world, port = 2, 31000 + os.getpid() % 2000
+    ctxm = mp.get_context("spawn")
+    q = ctxm.Queue()
+    procs = [ctxm.Process(target=_bn_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted(q.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, log, n_outs, collectives in results:
+        assert n_outs == 2 and collectives == 2
+        bn = [e for e in log if e[0] == "bn"]
+        assert [e[2] for e in bn] == [0, 1, 2] and all(e[3:6] == (4, 8, 4 * rank) for e in bn)
+        # phase 1 sees the column sums of both ranks (1 + 2), phase 2 also the summed squares (2 + 4)
+        assert bn[1][6][0] == [3.0] * 5
+        assert bn[2][6] == [[3.0] * 5, [6.0] * 5]
+        assert ("forward", 1, 4, 4 * rank) in log                 # the block after it runs the ordinary forward
+
+
+def test_batchnorm_output_block_is_rejected_under_data_parallelism():
+    sys.path.insert(0, ROOT)
+    from soklyn_b200 import log as sklog
+    from soklyn_b200.dp import DataParallelFFN
+    from soklyn_b200.ffn import FeedForwardNetwork
+    from soklyn_b200.function import Normalisation
+    layers = [_Layer(6, 5, 0, []), _Layer(5, 3, 1, [])]
+    layers[1].norm = Normalisation.BatchNorm
+    with pytest.raises(sklog.InvalidConfiguration):
+        DataParallelFFN(_Ctx(0, []), FeedForwardNetwork(layers, 6), global_batch=8, rank=0, world=2, scheme="allreduce")
