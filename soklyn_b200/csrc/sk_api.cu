@@ -170,6 +170,7 @@ cudaError_t run_gemm(sk_ctx *c, uint32_t dtype, const TA *A, size_t lda, const T
 }
 
 inline bool aligned16(const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
+constexpr uint32_t kSmallBatchRows = 256;   // up to here column sums and the vector step share one launch
 constexpr uint32_t kColsumFold = 8;   // slabs the per-32-row column sums of the dX epilogue are folded into
 
 Optim make_optim(const sk_optim *o, uint32_t step) {
@@ -339,7 +340,7 @@ int hidden_error_impl(sk_ctx *c, const sk_dense *cur, const sk_dense *next, uint
     c->fused_colsum_key = nullptr;
     const bool specialised = !f32 && ((cur->act == SK_ACT_SILU && cur->norm == SK_NORM_RMS) ||
                                       (cur->act == SK_ACT_MISH && cur->norm == SK_NORM_LAYER));
-    if ((c->in_ffn_backward || c->colsum_handover) && specialised && epi.vec_ok && tc_eligible(c, cur->dtype, dy, ec, wn, ec)) {
+    if ((c->in_ffn_backward || c->colsum_handover) && specialised && batch > kSmallBatchRows && epi.vec_ok && tc_eligible(c, cur->dtype, dy, ec, wn, ec)) {
         const uint32_t groups = (batch + 31) / 32;
         const size_t need = ((size_t)groups + kColsumFold) * 3 * cur->N * sizeof(float);
         if (need <= c->workspace_bytes) {
@@ -412,16 +413,41 @@ const float *column_sum_slabs(sk_ctx *c, const sk_dense *L, uint32_t batch, uint
 }
 
 template <typename T>
+VectorParams<T> vector_params(const sk_dense *L, const Optim &lin, const Optim &nrm, const Hyper &hyp) {
+    return VectorParams<T>{(T *)L->b, master_of<T>(L->master_b, L->b), L->dv_b, L->dm_b,
+                           (T *)L->norm_w, master_of<T>(L->master_norm_w, L->norm_w), L->dv_norm_w, L->dm_norm_w,
+                           (T *)L->norm_b, master_of<T>(L->master_norm_b, L->norm_b), L->dv_norm_b, L->dm_norm_b,
+                           L->norm != SK_NORM_BATCH, L->norm, lin, nrm, hyp};
+}
+
+template <typename T>
 int vector_update_launch(sk_ctx *c, const sk_dense *L, const float *partial, uint32_t nblocks, const Optim &lin,
                          const Optim &nrm, const Hyper &hyp) {
     ProfScope ps(c, SK_PROF_UPDATE);
-    vector_update_kernel<T><<<(L->N + 127) / 128, 128, 0, c->stream>>>(
-        partial, nblocks, L->N, (T *)L->b, master_of<T>(L->master_b, L->b), L->dv_b, L->dm_b,
-        (T *)L->norm_w, master_of<T>(L->master_norm_w, L->norm_w), L->dv_norm_w, L->dm_norm_w,
-        (T *)L->norm_b, master_of<T>(L->master_norm_b, L->norm_b), L->dv_norm_b, L->dm_norm_b,
-        L->norm != SK_NORM_BATCH, L->norm, lin, nrm, hyp);
+    vector_update_kernel<T><<<(L->N + 127) / 128, 128, 0, c->stream>>>(partial, nblocks, L->N, vector_params<T>(L, lin, nrm, hyp));
     c->launches++;
     return check_cuda(c, cudaGetLastError(), "bias / norm parameter step");
+}
+
+// Column sums + bias / normalisation-parameter step of a block. Small batches take both in one
+// launch; otherwise the sums come from the dX epilogue or the two-stage column-sum kernel.
+template <typename T>
+int column_sums_and_vector_update(sk_ctx *c, const sk_dense *L, uint32_t batch, const Optim &lin, const Optim &nrm,
+                                  const Hyper &hyp) {
+    const bool handed = c->fused_colsum_key && c->fused_colsum_key == L->d_prenorm && c->fused_colsum_batch == batch;
+    if (!handed && batch <= kSmallBatchRows) {
+        c->fused_colsum_key = nullptr;
+        ProfScope ps(c, SK_PROF_UPDATE);
+        colsum_update_kernel<T><<<(L->N + 31) / 32, kRowThreads, 0, c->stream>>>(L->d_prenorm, L->d_norm_w, L->d_norm_b, batch,
+                                                                             L->N, vector_params<T>(L, lin, nrm, hyp));
+        c->launches++;
+        return check_cuda(c, cudaGetLastError(), "column sums + bias / norm parameter step");
+    }
+    int rc = SK_OK;
+    uint32_t nslabs = 0;
+    const float *slabs = column_sum_slabs(c, L, batch, &nslabs, &rc);
+    if (rc) return rc;
+    return vector_update_launch<T>(c, L, slabs, nslabs, lin, nrm, hyp);
 }
 
 template <typename T>
@@ -430,10 +456,7 @@ int backward_update_impl(sk_ctx *c, const sk_dense *L, const void *x, uint32_t b
     const Optim lin = make_optim(lin_, step), nrm = make_optim(nrm_, step);
     const Hyper hyp{lr, clamp, 1.0f / (float)batch, L->regu, L->regu_coeff};
     int rc = SK_OK;
-    uint32_t nslabs = 0;
-    const float *slabs = column_sum_slabs(c, L, batch, &nslabs, &rc);
-    if (rc) return rc;
-    if ((rc = vector_update_launch<T>(c, L, slabs, nslabs, lin, nrm, hyp))) return rc;
+    if ((rc = column_sums_and_vector_update<T>(c, L, batch, lin, nrm, hyp))) return rc;
     const bool f32 = L->dtype == SK_F32;
     EpiWeightUpdate<T> epi{};
     epi.w = (T *)L->w; epi.master = master_of<T>(L->master_w, L->w); epi.dv = L->dv_w; epi.dm = L->dm_w;

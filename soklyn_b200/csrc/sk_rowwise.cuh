@@ -401,30 +401,68 @@ __global__ void colsum_final_kernel(const float *__restrict__ partial, float *__
     colsums[i] = t;
 }
 
-// Bias and normalisation-parameter step from the column sums (ffn/backward.cu:196-224).
-// `nblocks` partial slabs are summed first (pass 1 and a [3 x N] array for finished sums).
+// Bias and normalisation-parameter step of one column from its three sums (ffn/backward.cu:196-224).
+template <typename T> struct VectorParams {
+    T *b; float *master_b, *dv_b, *dm_b;
+    T *nw; float *master_nw, *dv_nw, *dm_nw;
+    T *nb; float *master_nb, *dv_nb, *dm_nb;
+    uint32_t use_bias, norm;
+    Optim lin, nrm;
+    Hyper hyp;
+};
 template <typename T>
-__global__ void vector_update_kernel(const float *__restrict__ partial, uint32_t nblocks, uint32_t N,
-                                     T *b, float *master_b, float *dv_b, float *dm_b,
-                                     T *nw, float *master_nw, float *dv_nw, float *dm_nw,
-                                     T *nb, float *master_nb, float *dv_nb, float *dm_nb,
-                                     uint32_t use_bias, uint32_t norm, Optim lin, Optim nrm, Hyper hyp) {
+__device__ __forceinline__ void vector_step(const VectorParams<T> &P, uint32_t col, const float (&s)[3]) {
+    auto step = [&](T *p, float *master, float *dv, float *dm, float sum, const Optim &o) {
+        float v = dv[col], m = dm[col];
+        const float np = optimiser_step(master[col], v, m, sum * kLossScaleInv, o, P.hyp, false);
+        dv[col] = v; dm[col] = m; master[col] = np;
+        if ((void *)p != (void *)master) p[col] = from_f32<T>(np);
+    };
+    if (P.use_bias) step(P.b, P.master_b, P.dv_b, P.dm_b, s[0], P.lin);
+    if (P.norm > 0) {
+        step(P.nw, P.master_nw, P.dv_nw, P.dm_nw, s[1], P.nrm);
+        if (P.norm > 1) step(P.nb, P.master_nb, P.dv_nb, P.dm_nb, s[2], P.nrm);
+    }
+}
+
+// `nblocks` partial slabs [3 x N] are summed first (1 slab for finished sums), then the step.
+template <typename T>
+__global__ void vector_update_kernel(const float *__restrict__ partial, uint32_t nblocks, uint32_t N, VectorParams<T> P) {
     const uint32_t col = blockIdx.x * blockDim.x + threadIdx.x;
     if (col >= N) return;
     float s[3] = {0.0f, 0.0f, 0.0f};
     for (uint32_t k = 0; k < nblocks; ++k)
 #pragma unroll
         for (int w = 0; w < 3; ++w) s[w] += partial[((size_t)k * 3 + w) * N + col];
-    auto step = [&](T *p, float *master, float *dv, float *dm, float sum, const Optim &o) {
-        float v = dv[col], m = dm[col];
-        const float np = optimiser_step(master[col], v, m, sum * kLossScaleInv, o, hyp, false);
-        dv[col] = v; dm[col] = m; master[col] = np;
-        if ((void *)p != (void *)master) p[col] = from_f32<T>(np);
-    };
-    if (use_bias) step(b, master_b, dv_b, dm_b, s[0], lin);
-    if (norm > 0) {
-        step(nw, master_nw, dv_nw, dm_nw, s[1], nrm);
-        if (norm > 1) step(nb, master_nb, dv_nb, dm_nb, s[2], nrm);
+    vector_step<T>(P, col, s);
+}
+
+// Small batches: column sums and the step in one launch. One block per 32 columns, its 8 row lanes
+// walk all M rows (same layout and summation order as colsum_partial_kernel with one row block).
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+colsum_update_kernel(const float *__restrict__ d_prenorm, const float *__restrict__ d_norm_w,
+                     const float *__restrict__ d_norm_b, uint32_t M, uint32_t N, VectorParams<T> P) {
+    __shared__ float red[3][8][33];
+    const uint32_t cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+    const uint32_t col = blockIdx.x * 32 + cx;
+    float sb = 0.0f, sw = 0.0f, sn = 0.0f;
+    if (col < N)
+        for (uint32_t r = ry; r < M; r += 8) {
+            const size_t idx = (size_t)r * N + col;
+            sb += d_prenorm[idx];
+            if (P.norm > 0) sw += d_norm_w[idx];
+            if (P.norm > 1) sn += d_norm_b[idx];
+        }
+    red[0][ry][cx] = sb; red[1][ry][cx] = sw; red[2][ry][cx] = sn;
+    __syncthreads();
+    if (ry == 0 && col < N) {
+        float s[3] = {0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int w = 0; w < 3; ++w)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s[w] += red[w][i][cx];
+        vector_step<T>(P, col, s);
     }
 }
 
