@@ -171,6 +171,7 @@ cudaError_t run_gemm(sk_ctx *c, uint32_t dtype, const TA *A, size_t lda, const T
 
 inline bool aligned16(const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
 constexpr uint32_t kSmallBatchRows = 256;   // up to here column sums and the vector step share one launch
+constexpr uint32_t kHandoverMinRows = 1024;  // below this a separate column-sum pass costs less than the heavier dX epilogue
 constexpr uint32_t kColsumFold = 8;   // slabs the per-32-row column sums of the dX epilogue are folded into
 
 Optim make_optim(const sk_optim *o, uint32_t step) {
@@ -340,7 +341,7 @@ int hidden_error_impl(sk_ctx *c, const sk_dense *cur, const sk_dense *next, uint
     c->fused_colsum_key = nullptr;
     const bool specialised = !f32 && ((cur->act == SK_ACT_SILU && cur->norm == SK_NORM_RMS) ||
                                       (cur->act == SK_ACT_MISH && cur->norm == SK_NORM_LAYER));
-    if ((c->in_ffn_backward || c->colsum_handover) && specialised && batch > kSmallBatchRows && epi.vec_ok && tc_eligible(c, cur->dtype, dy, ec, wn, ec)) {
+    if ((c->in_ffn_backward || c->colsum_handover) && specialised && batch > kHandoverMinRows && epi.vec_ok && tc_eligible(c, cur->dtype, dy, ec, wn, ec)) {
         const uint32_t groups = (batch + 31) / 32;
         const size_t need = ((size_t)groups + kColsumFold) * 3 * cur->N * sizeof(float);
         if (need <= c->workspace_bytes) {
