@@ -1,7 +1,7 @@
 """Build the reference's own CUDA kernels and their launcher into oracle/_ref/.
 
-TEST INFRASTRUCTURE, NOT PRODUCT. Needs the reference tree (SOKLYN_REF_DIR, default
-/root/reference); nothing is copied from it. Outputs, all git-ignored:
+TEST INFRASTRUCTURE, NOT PRODUCT. Needs a checkout of the reference, named by the
+environment variable SOKLYN_REF_DIR; nothing is copied from it. Outputs, all git-ignored:
   oracle/_ref/nn_math.ptx        reference src/cuda/nn_math.cu -> compute_75 PTX, the
                                  target of the reference's build.rs:15-18 (`-include
                                  cstdint` supplies uint32_t, which MSVC gets implicitly)
