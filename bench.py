@@ -25,21 +25,33 @@ import torch  # noqa: E402
 
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the three GEMM classes of the
-# default workload, from the ncu capture summarised in profiles/wide_ffn_step_ncu_full_b2048.md. That
-# capture ran the same network at batch 2048 (a full-size capture would hold too much device memory for
-# ncu's save/restore). Scaled to batch 8192 as: measured bytes + 3 x the bytes that grow with the batch
-# (activations in and out of the GEMM and its epilogue); weights, and for dW the 26 B per parameter of the
-# fused optimiser step, are the same at any batch. Averages over the launches of a class.
+# default workload, from one ncu capture of this network at batch 2048 (a full-size capture would hold
+# too much device memory for ncu's save/restore). Scaled to batch 8192 as: measured bytes + 3 x the bytes
+# that grow with the batch (activations in and out of the GEMM and its epilogue); weights, and for dW the
+# 26 B per parameter of the fused optimiser step, are the same at any batch. Averages over the launches
+# of a class. These cannot be measured inside an unprofiled run, hence constants.
 NCU_TRAFFIC_BYTES_PER_LAUNCH = {"gemm_forward": 545e6, "gemm_dx": 3017e6, "gemm_dw": 2166e6}
 
 
 def measured_peaks():
+    """Roofline denominators: the driver-written measurement of this pool's B200s when present."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
             p = json.load(f)
-        return {"hbm_gbs": p["hbm_gbs"], "tflops": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
-    return {"hbm_gbs": 6650.0, "tflops": 1400.0, "source": "fallback"}
+        return {"hbm_gbs": p["hbm_gbs"], "tflops_burst": p["bf16_tflops"],
+                "tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops_burst": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def pick_peak(peaks, timed_seconds, clocks):
+    """Which tensor peak a number is held against: the burst figure when the timed region was short and
+    the SM clock stayed near its maximum (a kernel timed as if alone), else the sustained one."""
+    sm, mx = (clocks or {}).get("sm_mhz"), (clocks or {}).get("sm_max_mhz")
+    near_max = sm is not None and mx and sm >= 0.95 * mx
+    if timed_seconds < 1.0 and near_max:
+        return peaks["tflops_burst"], "burst"
+    return peaks["tflops_sustained"], "sustained"
 
 
 class ClockSampler:
@@ -152,9 +164,11 @@ def run_ours(args):
     if args.batch:
         spec = configs.scaled(spec, batch=args.batch)
     ctx = sk.GpuContext(16, local_rank)
+    if args.lean:
+        ctx.set_lean_backward(True)
     local = spec.batch // world
     net = configs.build_network(ctx, spec, max_batch=local)
-    dp = DataParallelFFN(ctx, net, spec.batch, rank, world, scheme=args.dp_scheme)
+    dp = DataParallelFFN(ctx, net, spec.batch, rank, world, scheme=args.dp_scheme, chunks=args.dp_chunks)
     x, t, _ = configs.make_data(spec)
     r0 = rank * local
     prec = spec.prec()
@@ -192,28 +206,40 @@ def run_ours(args):
         sampler.start()
     launches0 = [0]
 
-    # Per-kernel-class device times come from CUDA events around every launch. For the large
-    # workload they are recorded inside the timed region itself (46 event records per 10 ms step);
-    # for the launch-bound small networks they would distort the step time, so those are profiled
-    # in a second pass of the same K steps.
-    prof_in_timed = spec.cfg >= 4
-
     def arm():   # runs after the warm-up
         launches0[0] = ctx.launch_count()
-        if prof_in_timed:
-            ctx.profile_enable(True)
 
     ms = timed_steps(step_resident, args.steps, args.warmup, world, device, before_timed=arm)
     launches = ctx.launch_count() - launches0[0]
     clocks = sampler.stop() if rank == 0 else None
-    if not prof_in_timed:
-        ctx.profile_enable(True)
-        for i in range(args.steps):
-            step_resident(args.warmup + args.steps + i + 1)
+    # Per-kernel-class device times come from CUDA events around every launch; they are taken in a
+    # second pass of the same K steps so that the event records stay out of the timed region.
+    ctx.profile_enable(True)
+    for i in range(args.steps):
+        step_resident(args.warmup + args.steps + i + 1)
     prof = ctx.profile_read()
     ctx.profile_enable(False)
     # the e2e warm-up must leave slot parity consistent: step numbers continue from the warm-up
     ms_e2e = timed_steps(step_e2e, args.steps, 2, world, device)
+
+    # Correctness carried in the line: the loss of one more forward pass on the resident inputs (the
+    # same host formula on every rank's rows, averaged), and under data parallelism the largest
+    # difference between any rank's weights and rank 0's, which must be zero.
+    outs = dp.forward(xd, False, 10 ** 6)
+    ctx.synchronize()
+    diff = (outs[-1].data[:local].float() - td.data[:local].float())
+    loss_t = (0.5 * (diff * diff).mean() if spec.loss == "mse" else torch.zeros((), device=device)).reshape(1).double()
+    w_diff = torch.zeros(1, device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(loss_t)
+        loss_t /= world
+        for layer in net.get_layers():
+            wt = layer.get_weights().data.float()
+            ref0 = wt.clone()
+            dist.broadcast(ref0, 0)
+            w_diff = torch.maximum(w_diff, (wt - ref0).abs().max().double().reshape(1))
+        dist.all_reduce(w_diff, op=dist.ReduceOp.MAX)
+    loss_after, w_diff = float(loss_t.item()), float(w_diff.item())
 
     if rank == 0:
         peaks = measured_peaks()
@@ -226,13 +252,18 @@ def run_ours(args):
                  "gemm_dx": sum(2.0 * m_local * spec.dims[i] * spec.dims[i + 1] for i in range(1, spec.layers))}
         n_l, t_ms = gemm[top]
         achieved = flops[top] * args.steps / (t_ms * 1e-3) / 1e12 if t_ms > 0 else 0.0
+        peak, peak_kind = pick_peak(peaks, ms * 1e-3, clocks)
+        per_class = {k: {"tflops": flops[k] * args.steps / (v[1] * 1e-3) / 1e12, "frac_burst": flops[k] * args.steps / (v[1] * 1e-3) / 1e12 / peaks["tflops_burst"],
+                         "frac_sustained": flops[k] * args.steps / (v[1] * 1e-3) / 1e12 / peaks["tflops_sustained"]}
+                     for k, v in gemm.items() if v[1] > 0}
         line = {
             "metric": "FFN train samples/s", "value": spec.batch / (per_step * 1e-3), "unit": "samples/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": spec.precision, "data": "synthetic (seeded N(0,1) inputs/targets, Xavier-uniform weights)",
-            "config": {"workload": spec.name, "global_batch": spec.batch, "parallelism": f"dp{world}", "exchange": ("fused" if dp.fused else "nccl") if world > 1 else "none",
-                       "params": spec.params(), "l2": "working set per step is far larger than L2 (126 MB)"},
+            "config": {"workload": spec.name, "global_batch": spec.batch, "parallelism": f"dp{world}", "exchange": dp.exchange_name(),
+                       "params": spec.params(), "lean": bool(args.lean),
+                       "l2": "working set per step is far larger than L2 (126 MB)"},
             "tflops_per_step": spec.flops_per_step() / 1e12,
             "tflops_achieved": spec.flops_per_step() / (per_step * 1e-3) / 1e12,
             "e2e": {"value": spec.batch / (ms_e2e / args.steps * 1e-3), "unit": "samples/s",
@@ -240,14 +271,22 @@ def run_ours(args):
                     "d2h_bytes_per_step": out_host.numel() * out_host.element_size()},
             "gpu_launches": int(launches),
             "clocks": clocks,
-            "roofline": {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": peaks["tflops"],
-                         "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get(top) if spec.cfg == 4 and world == 1 else None,
-                         "traffic_note": "bytes per launch: ncu capture at batch 2048, batch-proportional part scaled to 8192 (see profiles/)",
-                         "peak_source": peaks["source"] + " (bf16 matmul, sustained)",
-                         "launches": int(n_l), "ms_per_launch": t_ms / max(1, n_l)},
+            "roofline": {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": peak,
+                         "unit": "TFLOP/s", "frac": achieved / peak,
+                         "frac_burst": achieved / peaks["tflops_burst"], "frac_sustained": achieved / peaks["tflops_sustained"],
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get(top) if spec.cfg == 4 and world == 1 and not args.batch else None,
+                         "traffic_note": "bytes per launch: ncu capture at batch 2048, batch-proportional part scaled to 8192",
+                         "peak_source": f"{peaks['source']} bf16 matmul, {peak_kind} (timed region {ms * 1e-3:.2f} s)",
+                         "launches": int(n_l), "ms_per_launch": t_ms / max(1, n_l), "per_class": per_class},
             "kernel_ms_per_step": {k: v[1] / args.steps for k, v in prof.items()},
+            "loss_after": loss_after,
         }
+        if world > 1:
+            line["dp_check"] = {"max_abs_weight_diff_vs_rank0": w_diff, "loss_after": loss_after,
+                                "note": "every rank's 16-bit weights compared with rank 0's after the timed steps; "
+                                        "loss of one more forward pass over the whole batch"}
+        if world == 1 and spec.cfg == 4 and not args.no_gemm_sweep:
+            line["dense_block_gemm"] = gemm_sweep_rows(ctx, [16384], [1024, 4096, 8192], ["f16"], peaks)
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_leg(spec, args.cpu_rows)
         print(json.dumps(line), flush=True)
@@ -257,28 +296,20 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def run_gemm_sweep(args):
-    """BASELINE config 5: the three GEMMs of one DenseBlock in isolation, with their fused epilogues,
-    over M x K x N (forward with bias + activation, dX with the activation-derivative / mask epilogue,
-    dW with the column sums and the fused optimiser step). X, W, dY ~ N(0,1)/sqrt(K), seeded."""
+def gemm_sweep_rows(ctx, ms_list, kn_list, dtypes, peaks, index0: int = 0):
+    """The three GEMMs of one DenseBlock in isolation, with their fused epilogues, over M x K x N: forward
+    with bias + activation, dX with the activation-derivative / mask epilogue, dW with the column sums and
+    the fused optimiser step. X, W, dY ~ N(0,1)/sqrt(K), seeded. One record per (dtype, M, K, N)."""
     import soklyn_b200 as sk
     from soklyn_b200.configs import _GivenWeights
     from soklyn_b200.core import Tensor
-    device = torch.device("cuda", 0)
-    torch.cuda.set_device(device)
-    ctx = sk.GpuContext(16, 0)
-    peaks = measured_peaks()
     acts = [sk.Activation.ReLU, sk.Activation.SiLU, sk.Activation.Tanh]
-    ms_list = [int(v) for v in args.sweep_m.split(",")]
-    kn_list = [int(v) for v in args.sweep_kn.split(",")]
-    rows, idx = [], 0
-    for prec_name in args.sweep_dtypes.split(","):
+    rows, idx = [], index0
+    for prec_name in dtypes:
         prec = {"f16": sk.Precision.FP16, "f32": sk.Precision.FP32, "bf16": sk.Precision.BF16}[prec_name]
         for m in ms_list:
             for k in kn_list:
                 for n in kn_list:
-                    if prec_name == "f32" and float(m) * k * n > 2.8e11:
-                        continue   # the FFMA path at these sizes takes seconds per call
                     gen = torch.Generator(device="cpu").manual_seed(5000 + idx)
                     act = acts[idx % 3]
                     idx += 1
@@ -296,12 +327,13 @@ def run_gemm_sweep(args):
                            "dX": lambda: ctx.gpu_hidden_layer_error(blk, nxt, m),
                            "dW": lambda: ctx.gpu_backward_pass(blk, x, tc, 1)}
                     rec = {"dtype": prec_name, "M": m, "K": k, "N": n, "act": act.ordinal()}
+                    heavy = float(m) * k * n >= 1e12 or (prec_name == "f32" and float(m) * k * n > 2e11)
                     for name, fn in ops.items():
-                        for _ in range(3):
+                        for _ in range(1 if heavy else 3):
                             fn()
                         torch.cuda.synchronize()
                         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                        iters = 5 if float(m) * k * n < 1e12 else 2
+                        iters = 2 if heavy else 5
                         e0.record()
                         for _ in range(iters):
                             fn()
@@ -313,49 +345,80 @@ def run_gemm_sweep(args):
                     rows.append(rec)
                     del blk, nxt, x
                     torch.cuda.empty_cache()
+    sixteen = [r for r in rows if r["dtype"] != "f32"]
+    out = {"metric": "DenseBlock GEMM TFLOP/s", "unit": "TFLOP/s", "shapes": rows,
+           "timing": "CUDA events around back-to-back calls of one entry point after warm-up; every call streams "
+                     "operands and epilogue tensors larger than L2 for M >= 4096"}
+    if sixteen:
+        mean = sum(r["forward_tflops"] + r["dX_tflops"] + r["dW_tflops"] for r in sixteen) / (3 * len(sixteen))
+        out.update({"mean_16bit": mean, "frac_burst": mean / peaks["tflops_burst"], "frac_sustained": mean / peaks["tflops_sustained"],
+                    "best_forward": max(r["forward_tflops"] for r in sixteen)})
+    return out
+
+
+def run_gemm_sweep(args):
+    """BASELINE config 5: the whole M x K x N sweep in both precisions, one JSON line."""
+    import soklyn_b200 as sk
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    ctx = sk.GpuContext(16, 0)
+    peaks = measured_peaks()
+    ms_list = [int(v) for v in args.sweep_m.split(",")]
+    kn_list = [int(v) for v in args.sweep_kn.split(",")]
+    res = gemm_sweep_rows(ctx, ms_list, kn_list, args.sweep_dtypes.split(","), peaks)
+    rows = res["shapes"]
     big = [r for r in rows if r["dtype"] != "f32" and r["M"] >= 4096]
     best = max((r["forward_tflops"] for r in big), default=0.0)
     mean = sum(r["forward_tflops"] + r["dX_tflops"] + r["dW_tflops"] for r in big) / max(1, 3 * len(big))
+    f32 = [r for r in rows if r["dtype"] == "f32" and r["M"] >= 4096]
+    mean32 = sum(r["forward_tflops"] + r["dX_tflops"] + r["dW_tflops"] for r in f32) / max(1, 3 * len(f32))
     line = {"metric": "DenseBlock GEMM TFLOP/s", "value": mean, "unit": "TFLOP/s", "n_gpus": 1, "steps": 1, "warmup": 3,
             "higher_is_better": True, "dtype": args.sweep_dtypes, "data": "synthetic (seeded N(0,1)/sqrt(K))",
             "config": {"workload": "dense_block_gemm_sweep", "M": ms_list, "KN": kn_list,
                        "note": "value = mean over forward/dX/dW of the 16-bit cases with M >= 4096, fused epilogues included"},
-            "best_forward_tflops": best, "peak": peaks["tflops"], "frac_of_peak": mean / peaks["tflops"], "sweep": rows}
+            "best_forward_tflops": best, "peak_burst": peaks["tflops_burst"], "peak_sustained": peaks["tflops_sustained"],
+            "frac_burst": mean / peaks["tflops_burst"], "frac_sustained": mean / peaks["tflops_sustained"],
+            "mean_f32_tflops": mean32, "sweep": rows}
     print(json.dumps(line), flush=True)
     ctx.close()
 
 
 def run_reference(args):
     """The reference's own kernels (oracle/_ref: its unmodified nn_math.cu, JIT-ed from compute_75 PTX as its
-    build.rs targets) with its launch configuration and per-launch stream synchronisation, on a bounded
-    sample of the workload's batch. Falls back to the CPU port of the reference when oracle/_ref is absent."""
+    build.rs targets) with its launch configuration and its stream synchronisation after every launch, on
+    the whole batch of the workload, on ONE GPU (the reference is single-device): rank 0 runs, other ranks
+    leave. The reference has no CPU implementation of this path (every operation is a CUDA launch), so this is
+    its stock code path. The process loads oracle/_ref/libsoklyn_ref.so and not the product library; the
+    Python classes that sequence the layers are the host mirror of the reference's DenseBlock /
+    FeedForwardNetwork. Falls back to the CPU port of the reference when oracle/_ref is absent."""
     rank, local_rank, world = dist_env()
     if rank != 0:
         return
     from soklyn_b200 import configs
     spec = configs.CONFIGS[args.config if args.config in configs.CONFIGS else 4]
-    rows = args.ref_rows if args.ref_rows > 0 else (256 if spec.cfg == 4 else spec.batch)
+    if args.batch:
+        spec = configs.scaled(spec, batch=args.batch)
+    rows = args.ref_rows if args.ref_rows > 0 else spec.batch
     sample = configs.scaled(spec, batch=rows)
     from oracle import ref_kernels
-    if not ref_kernels.available():
+    if not ref_kernels.available() or not torch.cuda.is_available():
         cb = cpu_baseline_leg(spec, args.cpu_rows)
         line = {"impl": "reference", "metric": "FFN train samples/s", "value": cb["value"], "unit": "samples/s",
-                "n_gpus": world, "steps": 1, "warmup": 0, "ms_per_step": 1e3 * args.cpu_rows / cb["value"],
+                "n_gpus": 1, "steps": 1, "warmup": 0, "ms_per_step": 1e3 * args.cpu_rows / cb["value"],
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
                 "data": "synthetic", "config": {"workload": spec.name, "global_batch": spec.batch},
                 "cpu_baseline": cb, "e2e": {"value": cb["value"], "unit": "samples/s", "h2d_bytes_per_step": 0,
                                             "d2h_bytes_per_step": 0}}
         print(json.dumps(line), flush=True)
         return
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    import harness as H
-    from soklyn_b200.core import Tensor
+    from soklyn_b200.core import Tensor, reset_tensor_ids
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
     ctx = ref_kernels.RefContext(16, local_rank, sync_each_launch=True)
     w = configs.make_weights(sample)
     x, t, _ = configs.make_data(sample)
-    net = H.build_device(ctx, sample, w)
+    reset_tensor_ids(0)
+    net = configs.build_network(ctx, sample, w)
     xd = Tensor.from_cpu_vector(ctx, x, x.shape, sample.prec())
     td = Tensor.from_cpu_vector(ctx, t, t.shape, sample.prec())
     tc, lc = sample.train_context(), sample.loss_config()
@@ -364,18 +427,26 @@ def run_reference(args):
         outs = net.forward(ctx, xd, rows, sample.use_dropout, s)
         net.backward(ctx, outs, td, xd, lc, tc, s)
 
-    l0 = ctx.ref_launch_count()
-    ms = timed_steps(step, args.steps, args.warmup, 1, device)
+    l0 = [0]
+
+    def arm():
+        l0[0] = ctx.ref_launch_count()
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms = timed_steps(step, args.steps, args.warmup, 1, device, before_timed=arm)
+    clocks = sampler.stop()
     per_step = ms / args.steps
     val = rows / (per_step * 1e-3)
-    line = {"impl": "reference", "metric": "FFN train samples/s", "value": val, "unit": "samples/s", "n_gpus": world,
+    line = {"impl": "reference", "metric": "FFN train samples/s", "value": val, "unit": "samples/s", "n_gpus": 1,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": spec.precision, "data": "synthetic",
-            "config": {"workload": spec.name, "global_batch": spec.batch, "sample_rows": rows},
-            "gpu_launches": int(ctx.ref_launch_count() - l0),
+            "config": {"workload": spec.name, "global_batch": spec.batch, "rows_per_step": rows, "parallelism": "dp1",
+                       "note": "the reference is single-device: one GPU whatever --gpus says"},
+            "gpu_launches": int(ctx.ref_launch_count() - l0[0]), "clocks": clocks,
             "cpu_baseline": {"value": val, "unit": "samples/s", "cores": 1, "kind": "reference",
                              "sample": f"the reference's own CUDA kernels (it has no CPU path) on one B200, one host "
-                                       f"thread, {rows} of {spec.batch} rows per step, synchronising after every launch"},
+                                       f"thread, all {rows} rows per step, synchronising after every launch"},
             "e2e": {"value": val, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
     ctx.close()
@@ -391,9 +462,12 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="override the global batch (parity/debug runs)")
     ap.add_argument("--cpu-rows", type=int, default=256, help="rows of the batch the CPU baseline leg runs")
     ap.add_argument("--ref-rows", type=int, default=0,
-                    help="rows of the batch the reference arm runs per step (0: 256 for config 4, the whole batch otherwise)")
+                    help="rows of the batch the reference arm runs per step (0: the whole batch)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--dp-scheme", default="auto", choices=["auto", "fused", "sharded", "allreduce"],
+    ap.add_argument("--no-gemm-sweep", action="store_true", help="leave the M = 16384 DenseBlock GEMM shapes out of the line")
+    ap.add_argument("--lean", action="store_true", help="SK_OPTION_LEAN_BACKWARD (not the headline configuration)")
+    ap.add_argument("--dp-chunks", type=int, default=0, help="row blocks per layer of the pipelined exchange (0: automatic)")
+    ap.add_argument("--dp-scheme", default="auto", choices=["auto", "pipelined", "fused", "sharded", "allreduce"],
                     help="gradient exchange of the data-parallel runs (see soklyn_b200/dp.py)")
     ap.add_argument("--sweep-m", default="256,1024,4096,16384,65536")
     ap.add_argument("--sweep-kn", default="1024,4096,8192")

@@ -103,8 +103,15 @@ int sk_ctx_set_stream(sk_ctx *ctx, void *stream);
  * d_norm_w / d_norm_b in its GEMM epilogue and hand them, through the workspace, to the next call if
  * that call is sk_backward_update / sk_backward_grads_lp for the same layer and batch (any other call
  * drops them). The caller promises not to modify those three tensors between the two calls. Off by
- * default; sk_ffn_backward always does this internally, where nothing can come in between. */
-enum { SK_OPTION_GEMM_ENGINE = 0, SK_OPTION_COLSUM_HANDOVER = 1 };
+ * default; sk_ffn_backward always does this internally, where nothing can come in between.
+ * SK_OPTION_LEAN_BACKWARD: 1 = a hidden block whose column sums are taken in the dX epilogue (16-bit,
+ * batch > 1024, SiLU+RMSNorm or Mish+LayerNorm) does not store grad, the f32 d_prenorm, d_norm_w and
+ * d_norm_b (src/mlp.rs:273-276): nothing in the backward pass reads them again, the GEMMs read the
+ * 16-bit d_prenorm_lp. A deviation from the reference, whose getters expose those tensors
+ * (src/mlp.rs:446-454): they keep stale contents. Parameters come out bit-identical. Off by default.
+ * SK_OPTION_RESERVE_SMS: number of SMs the tensor-core GEMMs leave free, so that a kernel on another
+ * stream (the data-parallel exchange) can run beside them. 0 by default. */
+enum { SK_OPTION_GEMM_ENGINE = 0, SK_OPTION_COLSUM_HANDOVER = 1, SK_OPTION_LEAN_BACKWARD = 2, SK_OPTION_RESERVE_SMS = 3 };
 int sk_ctx_set_option(sk_ctx *ctx, uint32_t option, uint32_t value);
 /* Grow the scratch workspace; never called implicitly. */
 int sk_ctx_reserve(sk_ctx *ctx, size_t workspace_bytes);
@@ -217,6 +224,36 @@ int sk_apply_vector_update(sk_ctx *ctx, const sk_dense *layer, const float *cols
 int sk_reduce_update_broadcast(sk_ctx *ctx, const sk_dense *layer, void *const *peer_grad, uint32_t world,
                                uint32_t rank, void *const *peer_w, const sk_optim *linear, float learn_rate,
                                float grad_clamp, uint32_t step);
+/* Pipelined form of the same exchange, the whole backward pass of a network in one call (no counterpart;
+ * the order kept is the reference's, src/ffn.rs:113-166: every hidden delta reads the next layer's weights
+ * after their update). Each weight matrix is exchanged in `blocks` blocks of rows (sk_dp_blocks gives the
+ * count actually used for a shape: the largest <= blocks that splits evenly; 0 = the shape cannot be
+ * split); inside a block rank r owns rows [r*K/(blocks*world), (r+1)*K/(blocks*world)) and keeps f32
+ * masters and moments current for those rows only. Per block: the dW GEMM writes the block of the local
+ * 16-bit gradient, one kernel on a second stream (on SMs the GEMMs leave free) pulls the owned rows from
+ * every rank, adds them, steps them and stores the new 16-bit rows into every rank's weight tensor, and the
+ * dX GEMM of the layer below waits, inside its TMA producer, only for the blocks of rows its tile needs.
+ * The last block's kernel also adds the [3 x N] column sums of all ranks and steps bias and normalisation
+ * parameters. All waits are bounded (SK_ERR_DEVICE_TIMEOUT at the next sk_sync; a kernel whose wait gave up
+ * changes no weight). Per layer the caller provides, for every rank as mapped into this process: the gradient
+ * buffer T [K x N], the weight tensor T [K x N] (this rank's entry must be the block's `w`), sk_dp_flag_bytes()
+ * bytes of flag words (zero at set-up), and a column-sum buffer f32 [3 x N]. `epoch` must grow by one per call.
+ * 16-bit blocks without BatchNorm; world = 2, 4 or 8. When the call returns, later work on the context's
+ * stream is ordered after the whole exchange. */
+typedef struct {
+    void *const *peer_grad;
+    void *const *peer_w;
+    void *const *peer_flags;
+    void *const *peer_colsums;
+} sk_exchange;
+uint32_t sk_dp_blocks(uint32_t K, uint32_t N, uint32_t world, uint32_t blocks);
+uint32_t sk_dp_flag_bytes(void);
+int sk_dp_backward(sk_ctx *ctx, const sk_dense *const *layers, const sk_exchange *exchange, uint32_t n_layers,
+                   const void *target, uint32_t target_rows, const void *x, uint32_t x_rows, uint32_t loss,
+                   uint32_t loss_act, float loss_leaky, const sk_optim *linear, const sk_optim *norm_opt,
+                   uint32_t batch, uint32_t batch_stat, uint32_t world, uint32_t rank, uint32_t blocks,
+                   uint32_t epoch, float learn_rate, float grad_clamp, uint32_t step);
+
 /* Exchange arena of one rank: sk_peer_alloc allocates `bytes` of zeroed device memory (set-up time,
  * not the hot path) and returns a 64-byte CUDA IPC handle for it; the other ranks (other processes
  * on the same node) turn that handle into a pointer usable by kernels of THEIR device with

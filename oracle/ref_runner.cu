@@ -18,6 +18,7 @@
 #include <string>
 #include <vector>
 #include <cuda.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include "../include/soklyn_b200.h"
@@ -109,6 +110,26 @@ int ref_configure(void *stream, uint32_t tile_dim, int sync_each_launch) {
 }
 unsigned long long ref_launch_count(void) { return g_launches; }
 int ref_sync(void) { return cudaStreamSynchronize(g_stream) == cudaSuccess ? SK_OK : SK_ERR_DRIVER; }
+
+/* gpu_broadcast, src/io/device/util_device.rs:49-78, for Tensor::fill / zeroing. dtype as in sk_dense. */
+int ref_fill(void *dst, uint32_t dtype, float value, size_t len) {
+    if (len == 0) return SK_OK;
+    const uint32_t t2 = g_tile * g_tile;
+    const Dim grid{(uint32_t)((len + t2 - 1) / t2), 1}, block{t2, 1};
+    if (dtype == SK_F32) return launch("broadcast_kernel_f32", grid, block, 0, false, dst, value, (uint32_t)len);
+    if (dtype == SK_F16) return launch("broadcast_kernel_f16", grid, block, 0, false, dst, __float2half_rn(value), (uint32_t)len);
+    return SK_ERR_UNSUPPORTED_CAST;
+}
+
+/* gpu_cast_t, src/io/device/util_device.rs:7-47 */
+int ref_cast(const void *src, uint32_t src_dtype, void *dst, uint32_t dst_dtype, size_t len) {
+    if (len == 0) return SK_OK;
+    const uint32_t t2 = g_tile * g_tile;
+    const Dim grid{(uint32_t)((len + t2 - 1) / t2), 1}, block{t2, 1};
+    if (src_dtype == SK_F32 && dst_dtype == SK_F16) return launch("cast_f32_f16_t_kernel", grid, block, 0, false, src, dst, (uint32_t)len);
+    if (src_dtype == SK_F16 && dst_dtype == SK_F32) return launch("cast_f16_f32_t_kernel", grid, block, 0, false, src, dst, (uint32_t)len);
+    return SK_ERR_UNSUPPORTED_CAST;
+}
 
 /* src/io/device/ffn_device.rs:12-139 */
 int ref_dense_forward(const sk_dense *L, const void *x, uint32_t /*x_rows*/, uint32_t batch,

@@ -16,7 +16,7 @@ _CSRC = os.path.join(_PKG, "csrc")
 _LIB = os.path.join(_PKG, "lib", "libsoklyn_b200.so")
 _INCLUDE = os.path.join(os.path.dirname(_PKG), "include")
 
-NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "--split-compile=0",
               "-shared", "-Xcompiler", "-fPIC"]
 
 SK_F32, SK_F16, SK_BF16 = 0, 1, 2
@@ -47,6 +47,11 @@ class SkDense(C.Structure):
         + [("norm", C.c_uint32), ("act", C.c_uint32), ("leaky_coeff", C.c_float), ("regu", C.c_uint32),
            ("regu_coeff", C.c_float), ("mask_coeff", C.c_float), ("tensor_id", C.c_uint32)]
     )
+
+
+class SkExchange(C.Structure):
+    """Per-layer pointer tables of sk_dp_backward: arrays of `world` device pointers, one per rank."""
+    _fields_ = [("peer_grad", C.c_void_p), ("peer_w", C.c_void_p), ("peer_flags", C.c_void_p), ("peer_colsums", C.c_void_p)]
 
 
 def sources() -> list[str]:
@@ -127,6 +132,12 @@ _SIGS = {
                                          C.POINTER(SkOptim), C.c_float, C.c_float, C.c_uint32]),
     "sk_reduce_update_broadcast": (C.c_int, [C.c_void_p, C.POINTER(SkDense), C.c_void_p, C.c_uint32, C.c_uint32,
                                              C.c_void_p, C.POINTER(SkOptim), C.c_float, C.c_float, C.c_uint32]),
+    "sk_dp_blocks": (C.c_uint32, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]),
+    "sk_dp_flag_bytes": (C.c_uint32, []),
+    "sk_dp_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p,
+                                 C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, C.c_void_p, C.c_void_p, C.c_uint32,
+                                 C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, C.c_float,
+                                 C.c_uint32]),
     "sk_copy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
     "sk_peer_alloc": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p]),
     "sk_peer_open": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p)]),

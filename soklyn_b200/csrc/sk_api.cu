@@ -15,6 +15,7 @@
 #include <tuple>
 
 #include "sk_gemm_simt.cuh"
+#include "sk_exchange.cuh"
 #include "sk_gemm_tc.cuh"
 #include "sk_rowwise.cuh"
 
@@ -36,6 +37,14 @@ struct sk_ctx {
     void *encode_tiled = nullptr;          // cuTensorMapEncodeTiled, resolved through the runtime
     std::map<std::tuple<const void *, uint64_t, uint64_t, uint64_t, uint32_t, uint32_t>, CUtensorMap> tmaps;
     uint64_t tc_launches = 0;
+    uint32_t tc_group_n = 8;               // tile columns walked together (SK_TC_GROUP_N at context creation)
+    uint32_t reserve_sms = 0;              // SMs the tensor-core GEMMs leave free (for a concurrent exchange kernel)
+    bool lean = false;                     // SK_OPTION_LEAN_BACKWARD
+    // pipelined data-parallel backward
+    cudaStream_t comm_stream = nullptr;    // exchange kernels run here, beside the GEMMs
+    cudaEvent_t comm_done = nullptr;
+    uint32_t *dp_counters = nullptr;       // one completion counter per (layer, block), zero between launches
+    uint32_t dp_reserve_override = 0;      // SK_DP_RESERVE_SMS at context creation (0: by rank count)
     // Column sums handed from the dX epilogue to the weight update of the same layer. Only inside
     // sk_ffn_backward (nothing can touch the tensors or the workspace in between there).
     bool in_ffn_backward = false;
@@ -51,6 +60,9 @@ struct sk_ctx {
 
 namespace {
 using namespace sk;
+
+constexpr uint32_t kDpMaxLayers = 64;
+constexpr uint32_t kDpCounterWords = kDpMaxLayers * kMaxChunks;
 
 int fail(sk_ctx *c, int code, const char *fmt, ...) {
     if (c) {
@@ -71,7 +83,8 @@ int check_cuda(sk_ctx *c, cudaError_t e, const char *what) {
 struct ProfScope {
     sk_ctx *c;
     size_t slot = (size_t)-1;
-    ProfScope(sk_ctx *ctx, uint32_t cls) : c(ctx) {
+    cudaStream_t st;
+    ProfScope(sk_ctx *ctx, uint32_t cls, cudaStream_t on = nullptr) : c(ctx), st(on ? on : ctx->stream) {
         if (!c->profiling) return;
         if (c->ev_used * 2 + 2 > c->ev_pool.size()) {
             cudaEvent_t a, b;
@@ -80,9 +93,9 @@ struct ProfScope {
         }
         slot = c->ev_used++;
         c->ev_class[slot] = cls;
-        cudaEventRecord(c->ev_pool[2 * slot], c->stream);
+        cudaEventRecord(c->ev_pool[2 * slot], st);
     }
-    ~ProfScope() { if (slot != (size_t)-1) cudaEventRecord(c->ev_pool[2 * slot + 1], c->stream); }
+    ~ProfScope() { if (slot != (size_t)-1) cudaEventRecord(c->ev_pool[2 * slot + 1], st); }
 };
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -91,11 +104,12 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
 
 // 2-D TMA descriptor over a row-major 16-bit matrix: `inner` contiguous elements per row, `outer`
 // rows `ld` elements apart, fetched in boxes of 64 x box_outer with the 128-byte swizzle.
-const CUtensorMap *get_tmap(sk_ctx *c, const void *ptr, uint32_t dtype, uint64_t inner, uint64_t outer, uint64_t ld,
-                            uint32_t box_outer) {
+// The descriptor is returned by value: the cache may be cleared by the next lookup.
+bool get_tmap(sk_ctx *c, const void *ptr, uint32_t dtype, uint64_t inner, uint64_t outer, uint64_t ld,
+              uint32_t box_outer, CUtensorMap *out) {
     auto key = std::make_tuple(ptr, inner, outer, ld, box_outer, dtype);
     auto it = c->tmaps.find(key);
-    if (it != c->tmaps.end()) return &it->second;
+    if (it != c->tmaps.end()) { *out = it->second; return true; }
     if (c->tmaps.size() > 512) c->tmaps.clear();
     CUtensorMap m;
     const cuuint64_t gdim[2] = {inner, outer};
@@ -106,8 +120,16 @@ const CUtensorMap *get_tmap(sk_ctx *c, const void *ptr, uint32_t dtype, uint64_t
         &m, dtype == SK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
         const_cast<void *>(ptr), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return nullptr;
-    return &c->tmaps.emplace(key, m).first->second;
+    if (r != CUDA_SUCCESS) return false;
+    c->tmaps.emplace(key, m);
+    *out = m;
+    return true;
+}
+
+// SMs a tensor-core GEMM may occupy.
+inline uint32_t tc_sms(const sk_ctx *c) {
+    const uint32_t n = (uint32_t)c->num_sms;
+    return c->reserve_sms < n ? n - c->reserve_sms : 1u;
 }
 
 // Can the tensor-core kernel take these operands? (16-byte aligned bases, row pitches that are
@@ -118,23 +140,24 @@ bool tc_eligible(const sk_ctx *c, uint32_t dtype, const void *a, size_t lda, con
     return ok(a, lda) && ok(b, ldb);
 }
 
+// cudaFuncSetAttribute is per device: one bit per device ordinal and kernel instantiation.
 template <typename T, bool A_MN, bool B_MN, int BN, class Epi>
-cudaError_t launch_tc_bn(sk_ctx *c, const CUtensorMap *ta, const CUtensorMap *tb, uint32_t M, uint32_t N, uint32_t K,
-                         const Epi &epi) {
+cudaError_t launch_tc_bn(sk_ctx *c, const CUtensorMap &ta, const CUtensorMap &tb, uint32_t M, uint32_t N, uint32_t K,
+                         const Epi &epi, const TcGate &gate, uint32_t group_n) {
     using S = TcShape<BN>;
-    static bool attr_set = false;
+    static uint64_t attr_set[4] = {0, 0, 0, 0};   // devices 0..255
     auto kernel = gemm_tc_kernel<A_MN, B_MN, BN, Epi>;
-    if (!attr_set) {
+    const unsigned dev = (unsigned)c->device & 255u;
+    if (!(attr_set[dev >> 6] >> (dev & 63) & 1ull)) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes);
         if (e != cudaSuccess) return e;
-        attr_set = true;
+        attr_set[dev >> 6] |= 1ull << (dev & 63);
     }
     const uint32_t tiles = ((M + kTcBM - 1) / kTcBM) * ((N + BN - 1) / BN);
-    const uint32_t grid = tiles < (uint32_t)c->num_sms ? tiles : (uint32_t)c->num_sms;
+    const uint32_t sms = tc_sms(c);
+    const uint32_t grid = tiles < sms ? tiles : sms;
     const uint32_t idesc = tc::make_instr_desc(std::is_same<T, __nv_bfloat16>::value ? 1u : 0u, A_MN, B_MN, kTcBM, BN);
-    uint32_t group_n = 8;
-    if (const char *env = getenv("SK_TC_GROUP_N")) { const int v = atoi(env); if (v >= 1 && v <= 64) group_n = (uint32_t)v; }
-    kernel<<<grid, kTcThreads, S::kSmemBytes, c->stream>>>(*ta, *tb, M, N, K, idesc, group_n, epi, c->tc_err);
+    kernel<<<grid, kTcThreads, S::kSmemBytes, c->stream>>>(ta, tb, M, N, K, idesc, group_n, epi, gate, c->tc_err);
     c->tc_launches++;
     return cudaGetLastError();
 }
@@ -142,30 +165,39 @@ cudaError_t launch_tc_bn(sk_ctx *c, const CUtensorMap *ta, const CUtensorMap *tb
 // C[M x N] = A.B on the tensor cores. A_MN / B_MN: operand contiguous along M / N (else along K).
 template <typename T, bool A_MN, bool B_MN, class Epi>
 cudaError_t launch_gemm_tc(sk_ctx *c, uint32_t dtype, const T *A, size_t lda, const T *B, size_t ldb, uint32_t M,
-                           uint32_t N, uint32_t K, const Epi &epi) {
+                           uint32_t N, uint32_t K, const Epi &epi, const TcGate &gate = TcGate{}) {
+    const uint32_t sms = tc_sms(c);
     auto cost = [&](uint32_t bn) {
         const uint64_t tiles = (uint64_t)((M + kTcBM - 1) / kTcBM) * ((N + bn - 1) / bn);
-        return ((tiles + c->num_sms - 1) / c->num_sms) * bn;
+        return ((tiles + sms - 1) / sms) * bn;
     };
     // A 128-wide tile re-reads the A panel twice as often per flop and measured about 0.8 of the
     // 256-wide tile's rate at equal occupancy, so it has to save more than a fifth of the waves.
     const bool wide = N > 128 && cost(256) * 4 <= cost(128) * 5;
     const uint32_t bn = wide ? 256 : 128;
-    const CUtensorMap *ta = A_MN ? get_tmap(c, A, dtype, M, K, lda, 64) : get_tmap(c, A, dtype, K, M, lda, kTcBM);
-    const CUtensorMap *tb = B_MN ? get_tmap(c, B, dtype, N, K, ldb, 64) : get_tmap(c, B, dtype, K, N, ldb, bn);
-    if (!ta || !tb) return cudaErrorInvalidValue;
-    return wide ? launch_tc_bn<T, A_MN, B_MN, 256, Epi>(c, ta, tb, M, N, K, epi)
-                : launch_tc_bn<T, A_MN, B_MN, 128, Epi>(c, ta, tb, M, N, K, epi);
+    CUtensorMap ta, tb;
+    const bool ok_a = A_MN ? get_tmap(c, A, dtype, M, K, lda, 64, &ta) : get_tmap(c, A, dtype, K, M, lda, kTcBM, &ta);
+    const bool ok_b = B_MN ? get_tmap(c, B, dtype, N, K, ldb, 64, &tb) : get_tmap(c, B, dtype, K, N, ldb, bn, &tb);
+    if (!ok_a || !ok_b) return cudaErrorInvalidValue;
+    uint32_t group_n = c->tc_group_n;
+    if (gate.flags) {   // a group of tile columns must not reach into a block of rows that arrives later
+        const uint32_t per_chunk = gate.rows_per_chunk / bn;
+        if (per_chunk >= 1 && per_chunk < group_n) group_n = per_chunk;
+        if (per_chunk == 0) group_n = 1;
+    }
+    return wide ? launch_tc_bn<T, A_MN, B_MN, 256, Epi>(c, ta, tb, M, N, K, epi, gate, group_n)
+                : launch_tc_bn<T, A_MN, B_MN, 128, Epi>(c, ta, tb, M, N, K, epi, gate, group_n);
 }
 
 // Engine choice for one product of the DenseBlock path.
 template <typename TA, typename TB, bool A_KCONTIG, bool B_NCONTIG, class Epi>
 cudaError_t run_gemm(sk_ctx *c, uint32_t dtype, const TA *A, size_t lda, const TB *B, size_t ldb, uint32_t M, uint32_t N,
-                     uint32_t K, const Epi &epi) {
+                     uint32_t K, const Epi &epi, const TcGate &gate = TcGate{}) {
     if constexpr (std::is_same<TA, TB>::value && !std::is_same<TA, float>::value) {
         if (tc_eligible(c, dtype, A, lda, B, ldb))
-            return launch_gemm_tc<TA, !A_KCONTIG, B_NCONTIG, Epi>(c, dtype, A, lda, B, ldb, M, N, K, epi);
+            return launch_gemm_tc<TA, !A_KCONTIG, B_NCONTIG, Epi>(c, dtype, A, lda, B, ldb, M, N, K, epi, gate);
     }
+    if (gate.flags) return cudaErrorNotSupported;   // only the tensor-core kernel can wait for rows in flight
     return launch_gemm_simt<TA, TB, A_KCONTIG, B_NCONTIG, Epi>(c->stream, c->num_sms, A, lda, B, ldb, M, N, K, epi);
 }
 
@@ -317,12 +349,8 @@ int output_error_impl(sk_ctx *c, const sk_dense *L, const void *target, uint32_t
 }
 
 template <typename T>
-int hidden_error_impl(sk_ctx *c, const sk_dense *cur, const sk_dense *next, uint32_t batch, uint32_t batch_stat) {
-    if (batch < cur->max_batch) {
-        const size_t off = (size_t)batch * cur->N, bytes = (size_t)(cur->max_batch - batch) * cur->N * sizeof(float);
-        cudaMemsetAsync(cur->d_norm_w + off, 0, bytes, c->stream);
-        cudaMemsetAsync(cur->d_norm_b + off, 0, bytes, c->stream);
-    }
+int hidden_error_impl(sk_ctx *c, const sk_dense *cur, const sk_dense *next, uint32_t batch, uint32_t batch_stat,
+                      const TcGate &gate = TcGate{}) {
     const bool f32 = cur->dtype == SK_F32;
     EpiHidden<T> epi{};
     epi.predrop = (const T *)cur->predrop; epi.preact = (const T *)cur->preact; epi.mask = (const T *)cur->mask;
@@ -349,6 +377,12 @@ int hidden_error_impl(sk_ctx *c, const sk_dense *cur, const sk_dense *next, uint
             c->fused_colsum_key = cur->d_prenorm; c->fused_colsum_groups = groups; c->fused_colsum_batch = batch;
         }
     }
+    epi.lean = c->lean && epi.colsum_partial != nullptr;
+    if (!epi.lean && batch < cur->max_batch) {   // the reference zeroes d_norm_* first, which only shows in the rows beyond
+        const size_t off = (size_t)batch * cur->N, bytes = (size_t)(cur->max_batch - batch) * cur->N * sizeof(float);
+        cudaMemsetAsync(cur->d_norm_w + off, 0, bytes, c->stream);
+        cudaMemsetAsync(cur->d_norm_b + off, 0, bytes, c->stream);
+    }
     ProfScope ps(c, SK_PROF_GEMM_DX);
     cudaError_t e;
     // kernels specialised for the activation / normalisation pairs of the wide and the classifier networks
@@ -356,13 +390,13 @@ int hidden_error_impl(sk_ctx *c, const sk_dense *cur, const sk_dense *next, uint
         EpiHidden<T, SK_ACT_SILU, SK_NORM_RMS> se;
         static_assert(sizeof(se) == sizeof(epi), "specialised functor has the same fields");
         memcpy(&se, &epi, sizeof se);
-        e = run_gemm<T, T, true, false>(c, cur->dtype, dy, ec, wn, ec, batch, cur->N, ec, se);
+        e = run_gemm<T, T, true, false>(c, cur->dtype, dy, ec, wn, ec, batch, cur->N, ec, se, gate);
     } else if (!f32 && cur->act == SK_ACT_MISH && cur->norm == SK_NORM_LAYER) {
         EpiHidden<T, SK_ACT_MISH, SK_NORM_LAYER> se;
         memcpy(&se, &epi, sizeof se);
-        e = run_gemm<T, T, true, false>(c, cur->dtype, dy, ec, wn, ec, batch, cur->N, ec, se);
+        e = run_gemm<T, T, true, false>(c, cur->dtype, dy, ec, wn, ec, batch, cur->N, ec, se, gate);
     } else {
-        e = run_gemm<T, T, true, false>(c, cur->dtype, dy, ec, wn, ec, batch, cur->N, ec, epi);
+        e = run_gemm<T, T, true, false>(c, cur->dtype, dy, ec, wn, ec, batch, cur->N, ec, epi, gate);
     }
     int rc = check_cuda(c, e, "hidden error gemm");
     if (rc) c->fused_colsum_key = nullptr;
@@ -599,6 +633,135 @@ int apply_update_impl(sk_ctx *c, const sk_dense *L, const float *dw, const float
     return check_cuda(c, cudaGetLastError(), "weight step");
 }
 
+// ---- pipelined data-parallel backward ----------------------------------------------------------
+
+// Blocks of rows a [K x N] weight matrix is exchanged in: the largest count <= wanted for which every
+// rank owns whole rows of every block and its part is a whole number of 16-byte runs.
+uint32_t dp_chunks_for(uint32_t K, uint32_t N, uint32_t world, uint32_t wanted) {
+    if (wanted > (uint32_t)kMaxChunks) wanted = kMaxChunks;
+    for (uint32_t p = wanted; p >= 1; --p)
+        if (K % (p * world) == 0 && ((size_t)(K / (p * world)) * N) % 8 == 0 && (K / p) % 8 == 0) return p;
+    return 0;
+}
+
+// Rows [row0, row0 + nrows) of dW = X^T . dY in the storage type, divided by batch_stat (loss scale kept).
+template <typename T>
+int dw_rows_lp(sk_ctx *c, const sk_dense *L, const void *x, uint32_t batch, uint32_t batch_stat, void *g, uint32_t row0,
+               uint32_t nrows) {
+    T *out = (T *)g + (size_t)row0 * L->N;
+    EpiStoreScaled<T> epi{out, L->N, 1.0f / (float)batch_stat, L->N % 8 == 0 && aligned16(out)};
+    ProfScope ps(c, SK_PROF_GEMM_DW);
+    int rc = check_cuda(c, run_gemm<T, T, false, true>(c, L->dtype, (const T *)x + row0, L->K, (const T *)L->d_prenorm_lp,
+                                                        L->N, nrows, L->N, batch, epi), "weight gradient gemm (row block)");
+    c->launches++;
+    return rc;
+}
+
+template <typename T, int W>
+cudaError_t launch_exchange(sk_ctx *c, const ExchangeArgs<T> &a, uint32_t ctas) {
+    static uint64_t attr_set[4] = {0, 0, 0, 0};
+    constexpr int kSmem = 120 * 1024;   // more than half an SM's shared memory: one block per SM, none beside a GEMM block
+    auto kernel = exchange_chunk_kernel<T, W>;
+    const unsigned dev = (unsigned)c->device & 255u;
+    if (!(attr_set[dev >> 6] >> (dev & 63) & 1ull)) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+        if (e != cudaSuccess) return e;
+        attr_set[dev >> 6] |= 1ull << (dev & 63);
+    }
+    kernel<<<ctas, kExchangeThreads, kSmem, c->comm_stream>>>(a);
+    return cudaGetLastError();
+}
+
+template <typename T>
+int dp_backward_impl(sk_ctx *c, const sk_dense *const *layers, const sk_exchange *ex, uint32_t n, const void *target,
+                     uint32_t target_rows, const void *x, uint32_t x_rows, uint32_t loss, uint32_t loss_act,
+                     float loss_leaky, const sk_optim *lin_, const sk_optim *nrm_, uint32_t batch, uint32_t batch_stat,
+                     uint32_t world, uint32_t rank, uint32_t chunks, uint32_t epoch, float lr, float clamp, uint32_t step) {
+    const uint32_t last = n - 1;
+    uint32_t reserve = c->dp_reserve_override ? c->dp_reserve_override : (world <= 2 ? 8u : world <= 4 ? 16u : 20u);
+    if (reserve >= (uint32_t)c->num_sms) reserve = (uint32_t)c->num_sms / 4;
+    const uint32_t saved_reserve = c->reserve_sms;
+    c->reserve_sms = reserve;
+    int rc = sk_output_error(c, layers[last], target, target_rows, layers[last]->max_batch, loss, loss_act, loss_leaky);
+    uint32_t p_next = 0;   // blocks of layer i + 1
+    for (uint32_t ii = n; ii-- > 0 && rc == SK_OK;) {
+        const sk_dense *L = layers[ii];
+        const sk_exchange &E = ex[ii];
+        const void *in = ii == 0 ? x : layers[ii - 1]->out;
+        const uint32_t in_rows = ii == 0 ? x_rows : layers[ii - 1]->max_batch;
+        if ((rc = check_batch(c, L, in_rows, batch))) break;
+        if (ii < last) {
+            // delta of this layer from the next layer's weights: its rows arrive block by block
+            const sk_dense *nx = layers[ii + 1];
+            const uint32_t *flags_b = reinterpret_cast<const uint32_t *>(ex[ii + 1].peer_flags[rank]) + kMaxChunks * kMaxRanks;
+            TcGate gate{flags_b, world, (uint32_t)kMaxRanks, p_next, nx->K / p_next, epoch};
+            const bool gated = tc_eligible(c, L->dtype, nx->d_prenorm_lp, nx->N, nx->w, nx->N);
+            if (!gated) {
+                wait_words_kernel<<<1, 64, 0, c->stream>>>(flags_b, p_next, kMaxRanks, world, epoch, c->tc_err);
+                c->launches++; c->tc_launches++;
+            }
+            c->in_ffn_backward = true;
+            rc = hidden_error_impl<T>(c, L, nx, batch, batch_stat, gated ? gate : TcGate{});
+            c->in_ffn_backward = false;
+            if (rc) break;
+        }
+        // column sums of this rank's rows into its arena (the other ranks read them in the last block's kernel)
+        uint32_t nslabs = 0;
+        const float *slabs = column_sum_slabs(c, L, batch, &nslabs, &rc);
+        if (rc) break;
+        colsum_final_kernel<<<(3 * L->N + 255) / 256, 256, 0, c->stream>>>(slabs, (float *)E.peer_colsums[rank], L->N, nslabs);
+        c->launches++;
+        if ((rc = check_cuda(c, cudaGetLastError(), "column sums (final)"))) break;
+
+        const uint32_t P = dp_chunks_for(L->K, L->N, world, chunks);
+        const uint32_t rows_block = L->K / P, rows_own = rows_block / world;
+        const Optim lin = make_optim(&lin_[ii], step), nrm = make_optim(&nrm_[ii], step);
+        ExchangeArgs<T> a{};
+        PeerPtrs pf{};
+        for (uint32_t r = 0; r < world; ++r) {
+            a.grad.p[r] = E.peer_grad[r]; a.w.p[r] = E.peer_w[r]; a.flags.p[r] = E.peer_flags[r]; a.colsums.p[r] = E.peer_colsums[r];
+            pf.p[r] = E.peer_flags[r];
+        }
+        a.world = world; a.rank = rank; a.epoch = epoch;
+        a.master = master_of<T>(L->master_w, L->w); a.dv = L->dv_w; a.dm = L->dm_w;
+        a.opt = lin; a.hyp = Hyper{lr, clamp, 1.0f, L->regu, L->regu_coeff};
+        a.err = c->tc_err; a.N = L->N;
+        a.vp = vector_params<T>(L, lin, nrm, Hyper{lr, clamp, 1.0f / (float)batch_stat, L->regu, L->regu_coeff});
+        for (uint32_t ch = 0; ch < P && rc == SK_OK; ++ch) {
+            if ((rc = dw_rows_lp<T>(c, L, in, batch, batch_stat, E.peer_grad[rank], ch * rows_block, rows_block))) break;
+            signal_chunk_kernel<<<1, 32, 0, c->stream>>>(pf, world, (0 * kMaxChunks + ch) * kMaxRanks + rank, epoch);
+            c->launches++;
+            a.chunk = ch;
+            a.off = ((size_t)ch * rows_block + (size_t)rank * rows_own) * L->N;
+            a.len = (size_t)rows_own * L->N;
+            a.done = c->dp_counters + ii * kMaxChunks + ch;
+            a.do_vector = ch == P - 1;
+            ProfScope ps(c, SK_PROF_UPDATE, c->comm_stream);
+            cudaError_t e;
+            switch (world) {
+            case 2: e = launch_exchange<T, 2>(c, a, reserve); break;
+            case 4: e = launch_exchange<T, 4>(c, a, reserve); break;
+            case 8: e = launch_exchange<T, 8>(c, a, reserve); break;
+            default: e = cudaErrorInvalidValue;
+            }
+            c->launches++; c->tc_launches++;
+            rc = check_cuda(c, e, "exchange kernel");
+        }
+        p_next = P;
+    }
+    c->fused_colsum_key = nullptr;
+    c->reserve_sms = saved_reserve;
+    if (rc) return rc;
+    // the step is complete when this rank's exchange kernels have finished and every rank's rows of the
+    // first layer have landed here (the deltas above already waited for the other layers' rows)
+    cudaEventRecord(c->comm_done, c->comm_stream);
+    cudaStreamWaitEvent(c->stream, c->comm_done, 0);
+    const uint32_t *flags_b0 = reinterpret_cast<const uint32_t *>(ex[0].peer_flags[rank]) + kMaxChunks * kMaxRanks;
+    wait_words_kernel<<<1, 64, 0, c->stream>>>(flags_b0, p_next, kMaxRanks, world, epoch, c->tc_err);
+    c->launches++; c->tc_launches++;
+    return check_cuda(c, cudaGetLastError(), "end of the data-parallel backward pass");
+}
+
 #define SK_DISPATCH(dtype, fn, ...)                                        \
     ((dtype) == SK_F32 ? fn<float>(__VA_ARGS__)                            \
      : (dtype) == SK_F16 ? fn<__half>(__VA_ARGS__) : fn<__nv_bfloat16>(__VA_ARGS__))
@@ -632,6 +795,8 @@ int sk_ctx_create(int device, uint32_t tile_dim, void *stream, int create_stream
     cudaFuncSetAttribute(sk::norm_rows_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
     cudaFuncSetAttribute(sk::norm_rows_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
     c->cc_major = prop.major;
+    if (const char *env = getenv("SK_TC_GROUP_N")) { const int v = atoi(env); if (v >= 1 && v <= 64) c->tc_group_n = (uint32_t)v; }
+    if (const char *env = getenv("SK_DP_RESERVE_SMS")) { const int v = atoi(env); if (v >= 1 && v < c->num_sms) c->dp_reserve_override = (uint32_t)v; }
     {
         cudaDriverEntryPointQueryResult q;
         void *fn = nullptr;
@@ -640,10 +805,15 @@ int sk_ctx_create(int device, uint32_t tile_dim, void *stream, int create_stream
             c->encode_tiled = fn;
         if (cudaMalloc(&c->tc_err, sizeof(int)) == cudaSuccess) cudaMemset(c->tc_err, 0, sizeof(int));
         else c->tc_err = nullptr;
+        if (cudaMalloc(&c->dp_counters, kDpCounterWords * sizeof(uint32_t)) == cudaSuccess)
+            cudaMemset(c->dp_counters, 0, kDpCounterWords * sizeof(uint32_t));
+        else c->dp_counters = nullptr;
     }
     if (workspace_bytes == 0) workspace_bytes = (size_t)64 << 20;
     if (cudaMalloc(&c->workspace, workspace_bytes) != cudaSuccess) {
         if (c->own_stream) cudaStreamDestroy(c->stream);
+        if (c->tc_err) cudaFree(c->tc_err);
+        if (c->dp_counters) cudaFree(c->dp_counters);
         delete c;
         return SK_ERR_DRIVER;
     }
@@ -658,6 +828,9 @@ void sk_ctx_destroy(sk_ctx *c) {
     cudaStreamSynchronize(c->stream);
     if (c->workspace) cudaFree(c->workspace);
     if (c->tc_err) cudaFree(c->tc_err);
+    if (c->dp_counters) cudaFree(c->dp_counters);
+    if (c->comm_stream) { cudaStreamSynchronize(c->comm_stream); cudaStreamDestroy(c->comm_stream); }
+    if (c->comm_done) cudaEventDestroy(c->comm_done);
     for (cudaEvent_t e : c->ev_pool) cudaEventDestroy(e);
     if (c->own_stream) cudaStreamDestroy(c->stream);
     delete c;
@@ -706,6 +879,8 @@ int sk_ctx_set_option(sk_ctx *c, uint32_t option, uint32_t value) {
         c->fused_colsum_key = nullptr;
         return SK_OK;
     }
+    if (option == SK_OPTION_LEAN_BACKWARD && value <= 1) { c->lean = value != 0; return SK_OK; }
+    if (option == SK_OPTION_RESERVE_SMS && value < (uint32_t)c->num_sms) { c->reserve_sms = value; return SK_OK; }
     return fail(c, SK_ERR_INVALID_CONFIGURATION, "unknown option %u / value %u", option, value);
 }
 
@@ -965,6 +1140,62 @@ int sk_reduce_update_broadcast(sk_ctx *c, const sk_dense *L, void *const *peer_g
     if ((rc = check_exchange(c, L, peer_grad, world, rank))) return rc;
     if ((rc = check_exchange(c, L, peer_w, world, rank))) return rc;
     return SK_DISPATCH(L->dtype, reduce_update_broadcast_impl, c, L, peer_grad, world, rank, peer_w, lin, lr, clamp, step);
+}
+
+uint32_t sk_dp_blocks(uint32_t K, uint32_t N, uint32_t world, uint32_t wanted) {
+    if (world == 0 || wanted == 0) return 0;
+    return dp_chunks_for(K, N, world, wanted);
+}
+
+uint32_t sk_dp_flag_bytes(void) { return (uint32_t)(kFlagWordsPerLayer * sizeof(uint32_t)); }
+
+int sk_dp_backward(sk_ctx *c, const sk_dense *const *layers, const sk_exchange *ex, uint32_t n, const void *target,
+                   uint32_t target_rows, const void *x, uint32_t x_rows, uint32_t loss, uint32_t loss_act, float loss_leaky,
+                   const sk_optim *lin, const sk_optim *nrm, uint32_t batch, uint32_t batch_stat, uint32_t world,
+                   uint32_t rank, uint32_t blocks, uint32_t epoch, float lr, float clamp, uint32_t step) {
+    if (!c || !layers || !ex || !lin || !nrm || !target || !x) return SK_ERR_NULL_POINTER;
+    if (n == 0 || n > kDpMaxLayers) return fail(c, SK_ERR_INVALID_CONFIGURATION, "1 to %u layers", kDpMaxLayers);
+    if (!(world == 2 || world == 4 || world == 8) || rank >= world)
+        return fail(c, SK_ERR_INVALID_CONFIGURATION, "rank %u of %u ranks (2, 4 or 8)", rank, world);
+    if (blocks == 0) blocks = 4;
+    if (batch == 0 || batch_stat < batch) return fail(c, SK_ERR_INVALID_BATCH_SIZE, "local batch %u of %u rows", batch, batch_stat);
+    if (!c->tc_err || !c->dp_counters) return fail(c, SK_ERR_DRIVER, "context has no device error word / counters");
+    for (uint32_t i = 0; i < n; ++i) {
+        if (!layers[i]) return fail(c, SK_ERR_NULL_POINTER, "layer %u is NULL", i);
+        int rc = check_layer(c, layers[i], true);
+        if (rc) return rc;
+        const sk_dense *L = layers[i];
+        if (L->dtype == SK_F32 || L->dtype != layers[0]->dtype)
+            return fail(c, SK_ERR_INVALID_CONFIGURATION, "the pipelined exchange carries 16-bit blocks of one precision");
+        if (L->norm == SK_NORM_BATCH) return fail(c, SK_ERR_INVALID_CONFIGURATION, "BatchNorm blocks use the phased exchange");
+        if (i > 0 && L->K != layers[i - 1]->N)
+            return fail(c, SK_ERR_MISMATCHED_DIMENSIONS, "layer %u rows vs layer %u cols: expected %u, found %u", i, i - 1, layers[i - 1]->N, L->K);
+        if (lin[i].kind > 1 || nrm[i].kind > 1) return fail(c, SK_ERR_INVALID_CONFIGURATION, "optimiser ordinal out of range");
+        if (dp_chunks_for(L->K, L->N, world, blocks) == 0)
+            return fail(c, SK_ERR_MISMATCHED_DIMENSIONS, "%u weight rows do not split over %u ranks in whole 16-byte runs", L->K, world);
+        if (!ex[i].peer_grad || !ex[i].peer_w || !ex[i].peer_flags || !ex[i].peer_colsums)
+            return fail(c, SK_ERR_NULL_POINTER, "exchange tables of layer %u", i);
+        for (uint32_t r = 0; r < world; ++r)
+            if (!ex[i].peer_grad[r] || !ex[i].peer_w[r] || !ex[i].peer_flags[r] || !ex[i].peer_colsums[r] ||
+                reinterpret_cast<uintptr_t>(ex[i].peer_grad[r]) % 16 || reinterpret_cast<uintptr_t>(ex[i].peer_w[r]) % 16 ||
+                reinterpret_cast<uintptr_t>(ex[i].peer_colsums[r]) % 16)
+                return fail(c, SK_ERR_NULL_POINTER, "exchange pointer of layer %u, rank %u is NULL or unaligned", i, r);
+        if (ex[i].peer_w[rank] != L->w) return fail(c, SK_ERR_INVALID_CONFIGURATION, "layer %u: the weight tensor must be this rank's entry of peer_w", i);
+    }
+    if (cudaSetDevice(c->device) != cudaSuccess) return fail(c, SK_ERR_DRIVER, "cannot select device %d", c->device);
+    if (!c->comm_stream) {
+        int lo = 0, hi = 0;
+        cudaDeviceGetStreamPriorityRange(&lo, &hi);
+        if (cudaStreamCreateWithPriority(&c->comm_stream, cudaStreamNonBlocking, hi) != cudaSuccess ||
+            cudaEventCreateWithFlags(&c->comm_done, cudaEventDisableTiming) != cudaSuccess)
+            return fail(c, SK_ERR_DRIVER, "cannot create the exchange stream");
+    }
+    c->fused_colsum_key = nullptr;
+    return layers[0]->dtype == SK_F16
+               ? dp_backward_impl<__half>(c, layers, ex, n, target, target_rows, x, x_rows, loss, loss_act, loss_leaky, lin, nrm,
+                                          batch, batch_stat, world, rank, blocks, epoch, lr, clamp, step)
+               : dp_backward_impl<__nv_bfloat16>(c, layers, ex, n, target, target_rows, x, x_rows, loss, loss_act, loss_leaky,
+                                                 lin, nrm, batch, batch_stat, world, rank, blocks, epoch, lr, clamp, step);
 }
 
 int sk_peer_alloc(sk_ctx *c, size_t bytes, void **ptr, unsigned char handle_out[64]) {

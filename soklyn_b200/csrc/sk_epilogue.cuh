@@ -46,6 +46,15 @@ __device__ __forceinline__ void store_run(T *p, bool vec, const float (&in)[V]) 
     }
 }
 
+// f32 run stored with the evict-first hint: tensors that are written once and not read again by
+// the kernels that follow, so that they do not push operands of the running GEMM out of L2.
+template <int V>
+__device__ __forceinline__ void store_run_streaming(float *p, const float (&in)[V]) {
+    static_assert(V % 4 == 0, "whole 128-bit stores");
+#pragma unroll
+    for (int i = 0; i < V; i += 4) __stcs(reinterpret_cast<float4 *>(p + i), make_float4(in[i], in[i + 1], in[i + 2], in[i + 3]));
+}
+
 // Raw (unconverted) run of V elements, for loads issued ahead of their use.
 template <typename T, int V> __device__ __forceinline__ Pack<T, V> load_pack(const T *p) {
     return *reinterpret_cast<const Pack<T, V> *>(p);
@@ -168,6 +177,10 @@ template <typename T, int ACT = -1, int NORM = -1> struct EpiHidden {
     // kernel (every element then goes through finish()).
     float *colsum_partial;
     uint32_t colsum_groups;
+    // Lean backward: with the column sums taken here nothing in the backward pass reads grad, the f32
+    // d_prenorm, d_norm_w or d_norm_b again (the GEMMs read d_prenorm_lp), so their stores are skipped.
+    // Only set together with colsum_partial.
+    uint32_t lean;
     struct Acc { float dp[8], gw[8], gb[8]; };
 
     __device__ __forceinline__ uint32_t A() const { return ACT >= 0 ? (uint32_t)ACT : act; }
@@ -222,10 +235,19 @@ template <typename T, int ACT = -1, int NORM = -1> struct EpiHidden {
                 dp[j] = nw[j] * r * (gr[j] - gr[j] * inv - r * r * xv[j] * xv[j] * gr[j] * inv);
             }
         }
-        store_run<float, V>(grad + idx, true, gr);
-        store_run<float, V>(d_prenorm + idx, true, dp);
-        store_run<float, V>(d_norm_w + idx, true, gw);
-        store_run<float, V>(d_norm_b + idx, true, gb);
+        if (!lean) {
+            if constexpr (V % 4 == 0) {
+                store_run_streaming<V>(grad + idx, gr);
+                store_run_streaming<V>(d_prenorm + idx, dp);
+                store_run_streaming<V>(d_norm_w + idx, gw);
+                store_run_streaming<V>(d_norm_b + idx, gb);
+            } else {
+                store_run<float, V>(grad + idx, true, gr);
+                store_run<float, V>(d_prenorm + idx, true, dp);
+                store_run<float, V>(d_norm_w + idx, true, gw);
+                store_run<float, V>(d_norm_b + idx, true, gb);
+            }
+        }
         if (d_prenorm_lp) store_run<T, V>(d_prenorm_lp + idx, true, dp);
         if constexpr (V == 8) {
             if (sums && colsum_partial) {

@@ -53,7 +53,28 @@ template <class Epi> struct EpiAcc<Epi, std::enable_if_t<Epi::kHasAcc>> { static
 template <class Epi, class = void> struct EpiPingPong { static constexpr bool value = false; };
 template <class Epi> struct EpiPingPong<Epi, decltype((void)Epi::kPingPong)> { static constexpr bool value = Epi::kPingPong; };
 
-enum : int { kTcErrProducer = 1, kTcErrMma = 2, kTcErrEpilogue = 3 };
+enum : int { kTcErrProducer = 1, kTcErrMma = 2, kTcErrEpilogue = 3, kTcErrGate = 4 };
+
+// Optional gate on the B operand (data-parallel backward): the rows of B arrive from other GPUs in
+// `chunks` blocks of `rows_per_chunk` rows, and flags[chunk * stride + rank] reaches `epoch` once that
+// rank's part of the block has landed in this GPU's memory. The producer waits (bounded) for every rank's
+// flag of the blocks a tile needs before it issues the loads. flags == nullptr: no gate.
+struct TcGate {
+    const uint32_t *flags;
+    uint32_t world, stride, chunks, rows_per_chunk, epoch;
+};
+
+// Bounded wait until *flag (system-scope acquire) has reached `value` in wrap-around order.
+__device__ __forceinline__ bool wait_flag_reached(const uint32_t *flag, uint32_t value) {
+    const long long t0 = clock64();
+    for (;;) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if ((int32_t)(v - value) >= 0) return true;
+        if (clock64() - t0 > 4000000000LL) return false;
+        __nanosleep(100);
+    }
+}
 
 // Tile order. Tiles are walked in groups of group_n tile-columns (8 by default), row-major inside a group, so
 // that the ~148 tiles in flight form a compact block (about 18 x 8 tiles): the B panels of a group
@@ -70,7 +91,8 @@ __device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uin
 template <bool A_MN, bool B_MN, int BN, class Epi>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               uint32_t M, uint32_t N, uint32_t K, uint32_t idesc, uint32_t group_n, Epi epi, int *err_flag) {
+               uint32_t M, uint32_t N, uint32_t K, uint32_t idesc, uint32_t group_n, Epi epi, TcGate gate,
+               int *err_flag) {
     using S = TcShape<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -106,12 +128,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
-            bool ok = true;
+            uint32_t stage = 0, phase = 0, ready_chunks = 0;
+            bool ok = true, gate_ok = true;
             for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 uint32_t mi, ni;
                 tile_coords(tile, tiles_m, tiles_n, group_n, mi, ni);
                 const int32_t m0 = mi * kTcBM, n0 = ni * BN;
+                if (gate.flags) {
+                    // rows [n0, n0 + BN) of B: the blocks up to the one holding the tile's last row must be in
+                    const uint32_t last_row = min((uint32_t)n0 + BN, N) - 1;
+                    const uint32_t need = min(gate.chunks, last_row / gate.rows_per_chunk + 1);
+                    if (ready_chunks < need) {
+                        while (ready_chunks < need && gate_ok) {
+                            for (uint32_t r = 0; r < gate.world && gate_ok; ++r)
+                                gate_ok = wait_flag_reached(gate.flags + ready_chunks * gate.stride + r, gate.epoch);
+                            ++ready_chunks;
+                        }
+                        if (!gate_ok) { ok = false; break; }
+                        tc::fence_proxy_async_all();   // the rows were written through the generic proxy, TMA reads them
+                    }
+                }
                 for (uint32_t kb = 0; kb < num_kb; ++kb) {
                     if (!tc::mbar_wait(&empty_bar[stage], phase ^ 1)) { ok = false; break; }
                     tc::mbar_arrive_expect_tx(&full_bar[stage], S::kStageBytes);
@@ -132,7 +168,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     if (++stage == S::kStages) { stage = 0; phase ^= 1; }
                 }
             }
-            if (!ok) atomicCAS(err_flag, 0, kTcErrProducer);
+            if (!ok) atomicCAS(err_flag, 0, gate_ok ? kTcErrProducer : kTcErrGate);
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------

@@ -18,7 +18,9 @@
 //
 // The first call on each device looks the array's device address up (cudaGetSymbolAddress
 // with that device current) and caches it; make that first call outside any stream capture.
-// No call here allocates or frees memory.
+// The cache is a plain per-device pointer: host threads that race on a device's first call all
+// store the same value, which is harmless, but callers who want no data race at all should
+// make the first call per device from one thread. No call here allocates or frees memory.
 #include <cstdint>
 #include <cuda_runtime.h>
 
@@ -101,8 +103,8 @@ extern "C" int sk_column_sums_static(void *stream, const float *d_prenorm, const
 
     const uint32_t gx = (N + 31) / 32;
     uint32_t slabs = (4u * 148u + gx - 1) / gx;                         // enough blocks to cover the SMs
-    const uint32_t fit = (uint32_t)(kStaticFloats / ((size_t)3 * N));   // slabs the array can hold
-    if (slabs > fit) slabs = fit;
+    const uint32_t fit = (uint32_t)(kStaticFloats / ((size_t)3 * N));   // slabs the array can hold (>= 1, checked above)
+    if (slabs > fit) slabs = fit;                                       // wide N: fewer, taller slabs
     const uint32_t most = (batch + 7) / 8;
     if (slabs > most) slabs = most;
     if (slabs < 1) slabs = 1;

@@ -76,6 +76,15 @@ class GpuContext:
         follows it directly (the caller must not touch d_prenorm / d_norm_w / d_norm_b in between)."""
         self._check(self.lib.sk_ctx_set_option(self.handle, 1, int(on)))
 
+    def set_lean_backward(self, on: bool):
+        """Hidden blocks whose column sums are taken in the dX epilogue stop storing grad, the f32 d_prenorm,
+        d_norm_w and d_norm_b (a documented deviation from the reference's API-visible tensors)."""
+        self._check(self.lib.sk_ctx_set_option(self.handle, 2, int(on)))
+
+    def set_reserve_sms(self, count: int):
+        """SMs the tensor-core GEMMs leave free for a kernel on another stream."""
+        self._check(self.lib.sk_ctx_set_option(self.handle, 3, int(count)))
+
     def reserve(self, workspace_bytes: int):
         self._check(self.lib.sk_ctx_reserve(self.handle, workspace_bytes))
 
@@ -204,6 +213,25 @@ class GpuContext:
                                              loss_config.loss_func.value, act.ordinal(), act.coeff, lin, nrm,
                                              train_ctx.batch_size, train_ctx.learn_rate, train_ctx.grad_clamp,
                                              step & 0xFFFFFFFF))
+
+    # -- pipelined data-parallel backward: the whole pass in one native call --
+    def dp_blocks(self, k: int, n: int, world: int, wanted: int) -> int:
+        return int(self.lib.sk_dp_blocks(k, n, world, wanted))
+
+    def dp_flag_bytes(self) -> int:
+        return int(self.lib.sk_dp_flag_bytes())
+
+    def gpu_dp_backward(self, layers, tables, target: Tensor, input: Tensor, loss_config, train_ctx, batch: int,
+                        batch_stat: int, world: int, rank: int, blocks: int, epoch: int, step: int):
+        n = len(layers)
+        ptrs = (C.c_void_p * n)(*[C.addressof(l.desc()) for l in layers])
+        lin = (SkOptim * n)(*[_optim(o) for o in train_ctx.optimisers])
+        nrm = (SkOptim * n)(*[_optim(o) for o in train_ctx.norm_optimisers])
+        act = loss_config.activation
+        self._check(self.lib.sk_dp_backward(self.handle, ptrs, tables, n, target.ptr(), target.rows(), input.ptr(),
+                                            input.rows(), loss_config.loss_func.value, act.ordinal(), act.coeff, lin, nrm,
+                                            batch, batch_stat, world, rank, blocks, epoch & 0xFFFFFFFF,
+                                            train_ctx.learn_rate, train_ctx.grad_clamp, step & 0xFFFFFFFF))
 
     # -- fused exchange over peer-mapped buffers (no counterpart in the reference) --
     def gpu_reduce_update_broadcast(self, layer, peer_grad, world: int, rank: int, peer_w, train_ctx, step: int):

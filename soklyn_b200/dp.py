@@ -28,12 +28,29 @@ Two exchange schemes:
   All flag waits are bounded (SK_ERR_DEVICE_TIMEOUT instead of a hang). Only the small column sums
   still use an NCCL all-reduce.
 
+* "pipelined" (default for 16-bit networks without BatchNorm on 2, 4 or 8 GPUs of one node): the fused
+  exchange cut into blocks of weight rows and run beside the GEMMs. The whole backward pass is ONE native
+  call (sk_dp_backward): per block of rows the dW GEMM writes the local gradient, a kernel on a second
+  stream (on SMs the GEMMs leave free) pulls, adds, steps and redistributes the rows this rank owns, and the
+  dX GEMM of the layer below waits inside its TMA producer only for the blocks its tile needs. Column sums
+  travel through the same arena; no library collective is left on the step. Inside block c of a matrix with
+  K rows, rank r owns rows [c*K/P + r*K/(P*W), c*K/P + (r+1)*K/(P*W)) (`owned_row_ranges(i)`).
+
+Under every sharded scheme a rank's f32 master weights and moments are current only for the rows it owns.
+`gather_state()` (collective) makes them complete on every rank; call it before saving a checkpoint or
+converting a block, and `close()` calls it.
+
 BatchNorm blocks (hidden ones) run their forward in three phases around two all-reduces of the column
 statistics, so that mean and variance are those of the whole batch.
+
+Failure detection: device-side waits are bounded (SK_ERR_DEVICE_TIMEOUT). With `collective_timeout`
+(seconds) set, every library collective is waited for on the host with that deadline and a rank that never
+joins turns into log.DriverError on the others instead of a hang.
 """
 from __future__ import annotations
 
 import ctypes as C
+import datetime
 from typing import Sequence
 
 import torch
@@ -73,9 +90,12 @@ def shard_rows(global_batch: int, rank: int, world: int):
 
 class DataParallelFFN:
     def __init__(self, context, network: FeedForwardNetwork, global_batch: int, rank: int, world: int, group=None,
-                 scheme: str = "auto"):
+                 scheme: str = "auto", chunks: int = 0, collective_timeout: float | None = None):
         self.ctx, self.net, self.group = context, network, group
         self.rank, self.world, self.global_batch = rank, world, global_batch
+        self.collective_timeout = collective_timeout
+        self.pipelined = False
+        self.blocks = []
         self.row_offset, self.local_batch = shard_rows(global_batch, rank, world)
         # BatchNorm takes its column statistics over the whole batch: its forward runs in three phases
         # with two small all-reduces (hidden blocks only: the output-layer delta has no global 1/M).
@@ -107,14 +127,26 @@ class DataParallelFFN:
                 self.dw_shard.append(None)
         self.colsums = [torch.empty(3, l.get_weights().cols(), device=dev, dtype=torch.float32) for l in layers]
         self.collectives = 0
-        self.fused = scheme == "fused" or (scheme == "auto" and world > 1 and all(self.sharded) and world <= 8
-                                            and hasattr(context, "signal_peers"))
+        want = chunks if chunks > 0 else 4
+        can_pipeline = (world in (2, 4, 8) and hasattr(context, "gpu_dp_backward") and not self.bn_stats and bool(layers)
+                        and all(getattr(l, "precision", None) is not None and l.precision.value != 0 for l in layers)
+                        and all(context.dp_blocks(l.get_weights().rows(), l.get_weights().cols(), world, want) > 0 for l in layers))
+        if scheme == "pipelined" and not can_pipeline:
+            raise log.InvalidConfiguration("the pipelined exchange needs 2, 4 or 8 ranks and 16-bit blocks without BatchNorm "
+                                           "whose rows split evenly")
+        self.pipelined = can_pipeline and scheme in ("auto", "pipelined")
+        self.fused = not self.pipelined and (scheme == "fused" or (scheme == "auto" and world > 1 and all(self.sharded)
+                                                                   and world <= 8 and hasattr(context, "signal_peers")))
         self.epoch = 0
         if world > 1 and hasattr(context, "set_colsum_handover"):
             # backward() calls the delta of a layer and its weight-gradient GEMM back to back
             context.set_colsum_handover(True)
-        if self.fused:
-            self.dw, self.dw_shard = [], []      # the fused exchange stages gradients in its own arena
+        if self.pipelined:
+            self.sharded = [True] * len(layers)
+            self.blocks = [context.dp_blocks(l.get_weights().rows(), l.get_weights().cols(), world, want) for l in layers]
+            self.want_blocks = want
+        if self.fused or self.pipelined:
+            self.dw, self.dw_shard = [], []      # these exchanges stage gradients in their own arena
             self._map_peers(layers)
 
     def _map_peers(self, layers):
@@ -122,6 +154,7 @@ class DataParallelFFN:
         allocated by the library, exported as a CUDA IPC handle and mapped by every other rank with its
         own device current. Keeps pointer tables: staging / receive / flags of every rank per layer."""
         W, es = self.world, layers[0].get_weights().data.element_size()
+        flag_bytes = max(256, self.ctx.dp_flag_bytes() if hasattr(self.ctx, "dp_flag_bytes") else 256)
         offsets, total = [], 0
         for l in layers:
             nbytes = l.get_weights().rows() * l.get_weights().cols() * es
@@ -129,16 +162,17 @@ class DataParallelFFN:
             off_stage = total
             off_recv = off_stage + pad(nbytes)
             off_flags = off_recv + pad(nbytes)
-            total = off_flags + 256
-            offsets.append((off_stage, off_recv, off_flags, nbytes))
+            off_colsums = off_flags + pad(flag_bytes)
+            total = off_colsums + pad(3 * l.get_weights().cols() * 4)
+            offsets.append((off_stage, off_recv, off_flags, nbytes, off_colsums))
         self._arena, handle = self.ctx.peer_alloc(total)
         table = [None] * W
         dist.all_gather_object(table, handle, group=self.group)
         self._bases = [self._arena if r == self.rank else self.ctx.peer_open(table[r]) for r in range(W)]
         arr = lambda off: (C.c_void_p * W)(*[b + off for b in self._bases])
         self.stage_ptr, self.recv_ptr, self.flag_ptr, self.nbytes = [], [], [], []
-        self.p_stage, self.p_recv, self.p_flag_a, self.p_flag_b = [], [], [], []
-        for off_stage, off_recv, off_flags, nbytes in offsets:
+        self.p_stage, self.p_recv, self.p_flag_a, self.p_flag_b, self.p_colsums = [], [], [], [], []
+        for off_stage, off_recv, off_flags, nbytes, off_colsums in offsets:
             self.stage_ptr.append(self._arena + off_stage)
             self.recv_ptr.append(self._arena + off_recv)
             self.flag_ptr.append(self._arena + off_flags)
@@ -147,6 +181,7 @@ class DataParallelFFN:
             self.p_recv.append(arr(off_recv))
             self.p_flag_a.append(arr(off_flags))
             self.p_flag_b.append(arr(off_flags + 4 * W))
+            self.p_colsums.append(arr(off_colsums))
         # The receive buffer of a layer becomes the storage of its weight tensor: the owners' stores land
         # directly in every rank's weights and no copy is needed after the second handshake.
         self._own_w = []
@@ -160,8 +195,68 @@ class DataParallelFFN:
         torch.cuda.synchronize(self.ctx.device)
         dist.barrier(group=self.group)
 
+    def exchange_name(self) -> str:
+        if self.world == 1:
+            return "none"
+        return "pipelined" if self.pipelined else "fused" if self.fused else "nccl"
+
+    def _collective(self, fn, *args, **kwargs):
+        """A library collective on the context's stream; with `collective_timeout` set it is waited for on
+        the host and a rank that never joins becomes an error on the others."""
+        self.collectives += 1
+        if self.collective_timeout is None:
+            stream = getattr(self.ctx, "stream", None)
+            if stream is not None and self.ctx.device.type == "cuda":
+                with torch.cuda.stream(stream):   # the kernels around it run on this stream, not torch's current one
+                    return fn(*args, group=self.group, **kwargs)
+            return fn(*args, group=self.group, **kwargs)
+        work = fn(*args, group=self.group, async_op=True, **kwargs)
+        try:
+            done = work.wait(timeout=datetime.timedelta(seconds=self.collective_timeout))
+        except RuntimeError as e:
+            raise log.DriverError(f"collective did not complete within {self.collective_timeout} s: {e}") from e
+        if done is False:
+            raise log.DriverError(f"collective did not complete within {self.collective_timeout} s: a rank did not join")
+
+    def owned_row_ranges(self, i: int):
+        """[(first row, row count), ...] of layer i's weight matrix whose f32 masters and moments this rank keeps current."""
+        k = self.net.get_layers()[i].get_weights().rows()
+        if self.world > 1 and self.pipelined:
+            p = self.blocks[i]
+            own = k // (p * self.world)
+            return [(c * (k // p) + self.rank * own, own) for c in range(p)]
+        return [self.owned_rows(i)]
+
+    def gather_state(self):
+        """Collective: complete the f32 master weights and both moments of every sharded layer on every rank
+        (each rank contributes the rows it owns). After it, checkpoints and precision conversions see current
+        state everywhere (the contract of src/io/save.rs:227-346)."""
+        if self.world == 1:
+            return
+        if hasattr(self.ctx, "synchronize"):
+            self.ctx.synchronize()
+        for i, layer in enumerate(self.net.get_layers()):
+            if not self.sharded[i]:
+                continue
+            p = self.blocks[i] if self.pipelined else 1
+            for t in (layer.get_master_weights(), layer.get_dv_weights(), layer.get_dm_weights()):
+                if t is None:
+                    continue
+                k, n = t.data.shape
+                own = k // (p * self.world)
+                view = t.data.view(p, self.world, own * n)
+                mine = view[:, self.rank].contiguous()
+                parts = [torch.empty_like(mine) for _ in range(self.world)]
+                self._collective(dist.all_gather, parts, mine)
+                for r, part in enumerate(parts):
+                    view[:, r].copy_(part)
+
     def close(self):
-        """Unmap the other ranks' arenas and free this rank's (collective: every rank calls it)."""
+        """Complete the sharded optimiser state, unmap the other ranks' arenas and free this rank's
+        (collective: every rank calls it)."""
+        if self.world > 1 and any(self.sharded) and getattr(self, "_closed", False) is False:
+            self.gather_state()
+            self._closed = True
         if getattr(self, "_bases", None):
             torch.cuda.synchronize(self.ctx.device)
             dist.barrier(group=self.group)
@@ -198,17 +293,15 @@ class DataParallelFFN:
                     self.ctx.gpu_forward_batchnorm_phase(layer, cur, self.local_batch, self.global_batch, phase, stats,
                                                          use_dropout, step, self.row_offset)
                     if phase < 2:
-                        dist.all_reduce(stats[phase], group=self.group)
-                        self.collectives += 1
+                        self._collective(dist.all_reduce, stats[phase])
                 cur = layer.get_outputs()
             outputs.append(cur)
         return outputs
 
     def _exchange(self, i: int):
         if self.world > 1:
-            dist.all_reduce(self.dw[i], group=self.group)
-            dist.all_reduce(self.colsums[i], group=self.group)
-            self.collectives += 2
+            self._collective(dist.all_reduce, self.dw[i])
+            self._collective(dist.all_reduce, self.colsums[i])
 
     def backward(self, outputs: Sequence[Tensor], target: Tensor, input: Tensor, loss_config: LossConfig,
                  train_ctx: MultiLayerTrainContext, step: int):
@@ -223,6 +316,11 @@ class DataParallelFFN:
             return
         last = n - 1
         self.epoch += 1
+        if self.pipelined:
+            self.net._check_backward(target, input, loss_config, _LocalBatch(train_ctx, self.local_batch))
+            self.ctx.gpu_dp_backward(layers, self._exchange_tables(), target, input, loss_config, train_ctx, self.local_batch,
+                                     self.global_batch, self.world, self.rank, self.want_blocks, self.epoch, step)
+            return
         layers[last].compute_loss(self.ctx, target, loss_config)
         for i in range(last, -1, -1):
             layer = layers[i]
@@ -239,25 +337,44 @@ class DataParallelFFN:
                 self.ctx.gpu_backward_grads_lp(layer, x, self.local_batch, self.global_batch, self.stage_ptr[i],
                                                self.colsums[i])                 # dW into my arena's gradient buffer
                 self.ctx.signal_peers(self.p_flag_a[i], W, self.rank, e)       # my gradient buffer is complete
-                dist.all_reduce(self.colsums[i], group=self.group)
+                self._collective(dist.all_reduce, self.colsums[i])
                 self.ctx.wait_flags(self.flag_ptr[i], W, e)                     # so is everybody else's
                 self.ctx.gpu_reduce_update_broadcast(layer, self.p_stage[i], W, self.rank, self.p_recv[i], tci, step)
                 self.ctx.signal_peers(self.p_flag_b[i], W, self.rank, e)       # my rows are in every weight tensor
                 self.ctx.gpu_apply_vector_update(layer, self.colsums[i], self.global_batch, tci, step)
                 self.ctx.wait_flags(self.flag_ptr[i] + 4 * W, W, e)             # all rows of this layer have arrived
-                self.collectives += 1
                 continue
             if self.sharded[i]:
                 self.ctx.gpu_backward_grads_lp(layer, x, self.local_batch, self.global_batch, self.dw[i], self.colsums[i])
-                dist.reduce_scatter_tensor(self.dw_shard[i], self.dw[i], group=self.group)
-                dist.all_reduce(self.colsums[i], group=self.group)
+                self._collective(dist.reduce_scatter_tensor, self.dw_shard[i], self.dw[i])
+                self._collective(dist.all_reduce, self.colsums[i])
                 row0, nrows = self.owned_rows(i)
                 self.ctx.gpu_apply_update_rows(layer, self.dw_shard[i], row0, nrows, tci, step)
                 self.ctx.gpu_apply_vector_update(layer, self.colsums[i], self.global_batch, tci, step)
                 w = layer.get_weights().data
-                dist.all_gather_into_tensor(w, w[row0:row0 + nrows], group=self.group)
-                self.collectives += 3
+                self._collective(dist.all_gather_into_tensor, w, w[row0:row0 + nrows])
                 continue
             self.ctx.gpu_backward_grads(layer, x, self.local_batch, self.dw[i], self.colsums[i])
             self._exchange(i)
             self.ctx.gpu_apply_update(layer, self.dw[i], self.colsums[i], self.global_batch, tci, step)
+
+    def _exchange_tables(self):
+        """Per layer the four pointer tables sk_dp_backward takes (built once)."""
+        if getattr(self, "_tables", None) is None:
+            from ._native import SkExchange
+            n = len(self.p_stage)
+            tabs = (SkExchange * n)()
+            for i in range(n):
+                tabs[i].peer_grad = C.cast(self.p_stage[i], C.c_void_p)
+                tabs[i].peer_w = C.cast(self.p_recv[i], C.c_void_p)
+                tabs[i].peer_flags = C.cast(self.p_flag_a[i], C.c_void_p)
+                tabs[i].peer_colsums = C.cast(self.p_colsums[i], C.c_void_p)
+            self._tables = tabs
+        return self._tables
+
+
+class _LocalBatch:
+    """A MultiLayerTrainContext seen with this rank's row count (for the host-side shape checks)."""
+
+    def __init__(self, train_ctx, local_batch):
+        self.batch_size, self.optimisers = local_batch, train_ctx.optimisers

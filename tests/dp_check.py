@@ -29,7 +29,15 @@ def main():
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     ctx = sk.GpuContext(16, local)
     steps = 3
-    specs = [(configs.scaled(configs.CONFIGS[4], dims=(256, 512, 256, 512, 256), batch=256, name="dp_fused_f16"), "fused"),
+    specs = [(configs.scaled(configs.CONFIGS[4], dims=(256, 512, 256, 512, 256), batch=256, name="dp_pipelined_f16"), "pipelined"),
+             # per-rank batch above the row count from which the dX epilogue hands its column sums over, not a
+             # multiple of the 32-row groups, with the statistics batch different from the local one
+             (configs.scaled(configs.CONFIGS[4], dims=(128, 256, 128, 256, 128), batch=1100 * world, name="dp_pipelined_tall_f16"), "pipelined"),
+             (configs.scaled(configs.CONFIGS[3], dims=(384, 256, 128, 16), batch=64 * world, name="dp_pipelined_layernorm_dropout_f16"), "pipelined"),
+             # several tile columns per block of rows: the dX producer waits block by block
+             (configs.scaled(configs.CONFIGS[4], dims=(1024, 2048, 1024), batch=1024 * world, name="dp_pipelined_wide_f16"), "pipelined"),
+             (configs.scaled(configs.CONFIGS[4], dims=(128, 256, 128, 256, 128), batch=1100 * world, name="dp_fused_tall_f16"), "fused"),
+             (configs.scaled(configs.CONFIGS[4], dims=(256, 512, 256, 512, 256), batch=256, name="dp_fused_f16"), "fused"),
              (configs.scaled(configs.CONFIGS[4], dims=(256, 512, 256, 512, 256), batch=256, name="dp_sharded_f16"), "sharded"),
              (configs.scaled(configs.CONFIGS[3], dims=(384, 256, 128, 16), batch=128, name="dp_dropout_layernorm_f16"), "auto"),
              (configs.scaled(configs.CONFIGS[1], dims=(96, 64, 32, 10), batch=64, name="dp_allreduce_f32"), "auto"),
@@ -61,7 +69,18 @@ def main():
             ref = wt.clone()
             dist.broadcast(ref, 0)
             assert torch.equal(wt, ref), f"{spec.name}: layer {i} weights differ between ranks"
-        dp.close() if hasattr(dp, "close") else None
+        dp.close()   # also completes the sharded masters and moments on every rank (gather_state)
+        for i, layer in enumerate(net.get_layers()):
+            for getter in ("get_master_weights", "get_dv_weights", "get_dm_weights"):
+                t = getattr(layer, getter)()
+                if t is None:
+                    continue
+                ref = t.data.clone()
+                dist.broadcast(ref, 0)
+                assert torch.equal(t.data, ref), f"{spec.name}: layer {i} {getter} differs between ranks after gather_state"
+            if layer.get_master_weights() is not None:   # the 16-bit weights are the rounded masters, row for row
+                assert torch.equal(layer.get_master_weights().data.to(layer.get_weights().data.dtype), layer.get_weights().data), \
+                    f"{spec.name}: layer {i} weights are not the rounded master weights"
         if rank == 0:
             single, _ = H.run_device(ctx, spec, w, x, t, steps)
             tol = 1e-2 if spec.precision != "f32" else 5e-4
@@ -78,7 +97,8 @@ def main():
                 ma, mb = a.get_masks().download(ctx)[:per], b.get_masks().download(ctx)[:per]
                 mask_ok = np.array_equal(ma != 0, mb != 0)
                 print(f"{spec.name} L{i}: weights rel {rel:.2e} (max moved {moved.max():.2f} lr), outputs rel {rel_o:.2e}, "
-                      f"masks {'equal' if mask_ok else 'DIFFER'}, sharded={dp.sharded[i]}, fused={dp.fused}", flush=True)
+                      f"masks {'equal' if mask_ok else 'DIFFER'}, exchange={dp.exchange_name()}, blocks={dp.blocks[i] if dp.blocks else 1}",
+                      flush=True)
                 ok = ok and good and mask_ok and rel_o <= 5 * tol
     flag = torch.tensor([1 if ok else 0], device=ctx.device)
     dist.broadcast(flag, 0)

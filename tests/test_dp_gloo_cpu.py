@@ -185,3 +185,126 @@ def test_batchnorm_output_block_is_rejected_under_data_parallelism():
     layers[1].norm = Normalisation.BatchNorm
     with pytest.raises(sklog.InvalidConfiguration):
         DataParallelFFN(_Ctx(0, []), FeedForwardNetwork(layers, 6), global_batch=8, rank=0, world=2, scheme="allreduce")
+
+
+class _Data(_T):
+    """A fake tensor that also carries storage (what gather_state and the sharded schemes touch)."""
+
+    def __init__(self, data):
+        super().__init__(*data.shape)
+        self.data = data
+
+
+class _ShardedLayer(_Layer):
+    """16-bit block whose f32 masters and moments start as zeros; a rank marks the rows it owns."""
+
+    def __init__(self, k, n, idx, log):
+        super().__init__(k, n, idx, log)
+        from soklyn_b200.function import Precision
+        self.precision = Precision.FP16
+        self.w = _Data(torch.zeros(k, n, dtype=torch.float16))
+        self.master, self.dv, self.dm = (_Data(torch.zeros(k, n)) for _ in range(3))
+
+    def get_weights(self):
+        return self.w
+
+    def get_master_weights(self):
+        return self.master
+
+    def get_dv_weights(self):
+        return self.dv
+
+    def get_dm_weights(self):
+        return self.dm
+
+
+def _gather_worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from soklyn_b200.dp import DataParallelFFN
+    from soklyn_b200.ffn import FeedForwardNetwork
+    layers = [_ShardedLayer(8, 3, 0, []), _ShardedLayer(4, 5, 1, [])]
+    dp = DataParallelFFN(_Ctx(rank, []), FeedForwardNetwork(layers, 8), global_batch=8, rank=rank, world=world, scheme="sharded")
+    # pretend two blocks of rows per matrix, as the pipelined exchange lays them out
+    dp.pipelined, dp.blocks = True, [2, 1]
+    for i, layer in enumerate(layers):
+        for first, count in dp.owned_row_ranges(i):
+            for t, scale in ((layer.master, 1.0), (layer.dv, 10.0), (layer.dm, 100.0)):
+                t.data[first:first + count] = scale * (rank + 1) + torch.arange(first, first + count).float().unsqueeze(1) / 100
+    ranges = [dp.owned_row_ranges(i) for i in range(2)]
+    dp.gather_state()
+    q.put((rank, ranges, [(l.master.data.clone(), l.dv.data.clone(), l.dm.data.clone()) for l in layers]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_gather_state_completes_sharded_masters_and_moments_on_every_rank():
+    world, port = 2, 33000 + os.getpid() % 2000
+    ctxm = mp.get_context("spawn")
+    q = ctxm.Queue()
+    procs = [ctxm.Process(target=_gather_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted(q.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    (_, ranges0, state0), (_, ranges1, state1) = results
+    assert ranges0 == [[(0, 2), (4, 2)], [(0, 2)]] and ranges1 == [[(2, 2), (6, 2)], [(2, 2)]]
+    for (m0, v0, d0), (m1, v1, d1), k in zip(state0, state1, (8, 4)):
+        assert torch.equal(m0, m1) and torch.equal(v0, v1) and torch.equal(d0, d1)     # complete and identical
+        owner = torch.tensor([(1 if any(f <= r < f + c for f, c in rr) else 2)
+                              for r in range(k) for rr in [ranges0[0] if k == 8 else ranges0[1]]]).float()
+        rows = torch.arange(k).float() / 100
+        assert torch.allclose(m0[:, 0], owner + rows) and torch.allclose(v0[:, 0], 10 * owner + rows)
+        assert torch.allclose(d0[:, 0], 100 * owner + rows)
+
+
+def _absent_worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from soklyn_b200 import log as sklog
+    from soklyn_b200.context import LossConfig, MultiLayerTrainContext
+    from soklyn_b200.dp import DataParallelFFN
+    from soklyn_b200.ffn import FeedForwardNetwork
+    from soklyn_b200.function import Activation, LossFunc, Optimiser
+    log = []
+    layers = [_Layer(6, 5, 0, log), _Layer(5, 3, 1, log)]
+    dp = DataParallelFFN(_Ctx(rank, log), FeedForwardNetwork(layers, 6), global_batch=8, rank=rank, world=world,
+                         collective_timeout=2.0)
+    outs = dp.forward(_T(4, 6), False, 1)
+    opt = [Optimiser.Adam()] * 2
+    outcome = "skipped"
+    if rank == 0:       # rank 1 fails on the host before its first collective and never joins it
+        try:
+            dp.backward(outs, _T(4, 3), _T(4, 6), LossConfig(LossFunc.MeanSquareLoss, Activation.Identity),
+                        MultiLayerTrainContext(opt, opt, 8, 1e-3), 1)
+            outcome = "completed"
+        except sklog.DriverError as e:
+            outcome = "error: " + str(e)[:60]
+    q.put((rank, outcome, [e[0] for e in log]))
+    import time
+    time.sleep(0.5 if rank == 0 else 4.0)   # the absent rank stays alive past the other's deadline
+    os._exit(0)                             # no collective teardown: the group is broken by design
+
+
+def test_rank_that_never_joins_a_collective_becomes_an_error_after_the_host_deadline():
+    """Failure made on the host, no GPU involved: rank 1 skips its backward pass; rank 0's first gradient
+    all-reduce has nobody to meet and must end in an error status within the deadline, not hang."""
+    import time
+    world, port = 2, 35000 + os.getpid() % 2000
+    ctxm = mp.get_context("spawn")
+    q = ctxm.Queue()
+    procs = [ctxm.Process(target=_absent_worker, args=(r, world, port, q)) for r in range(world)]
+    t0 = time.time()
+    for p in procs:
+        p.start()
+    results = dict((r, (o, l)) for r, o, l in (q.get(timeout=60) for _ in range(world)))
+    assert time.time() - t0 < 45
+    for p in procs:
+        p.join(timeout=30)
+    assert results[1][0] == "skipped"
+    assert results[0][0].startswith("error: collective did not complete"), results[0]
+    assert "apply" not in results[0][1]          # nothing was stepped with a partial sum

@@ -53,8 +53,35 @@ def test_static_column_sums_match_context_path_twice(gpu_ctx, k, n, batch, norm_
         assert np.isfinite(a).all()
         scale = max(np.abs(b).max(), 1e-30)
         assert np.abs(a - b).max() / scale <= 1e-5   # the f32 tolerance of the parity tests
-        ref = blk.get_delta_prenorm_out().download(gpu_ctx)[:batch].astype(np.float64).sum(0)
-        assert np.abs(a[0] - ref).max() / max(np.abs(ref).max(), 1e-30) <= 1e-5
+        # all three rows against float64 column sums taken on the host
+        tensors = (blk.get_delta_prenorm_out(), blk.get_norm_weights_grad(), blk.get_norm_biases_grad())
+        for row, t in enumerate(tensors[: 1 + min(norm.ordinal(), 2)]):
+            ref = t.download(gpu_ctx)[:batch].astype(np.float64).sum(0)
+            assert np.abs(a[row] - ref).max() / max(np.abs(ref).max(), 1e-30) <= 1e-5, f"sum {row}"
+
+
+@pytest.mark.parametrize("n,batch", [(262144, 8), (200000, 40)])
+def test_static_column_sums_at_the_limit_of_the_array(gpu_ctx, n, batch):
+    """The widest N the built-in array can hold (one slab of partial sums fills it), and a width just below
+    it with more rows than one slab covers: two calls in a row against float64 sums taken on the host."""
+    import torch
+    from soklyn_b200 import _native
+    lib = _native.lib()
+    dev = gpu_ctx.device
+    stream = C.c_void_p(gpu_ctx.stream.cuda_stream)
+    for call in range(2):
+        g = torch.Generator(device="cpu").manual_seed(7 + call)
+        host = [torch.randn(batch, n, generator=g) * (call + 1) for _ in range(3)]
+        devs = [h.to(dev) for h in host]
+        got = torch.full((3, n), float("nan"), device=dev)
+        rc = lib.sk_column_sums_static(stream, devs[0].data_ptr(), devs[1].data_ptr(), devs[2].data_ptr(), got.data_ptr(),
+                                       batch, n, 2)
+        assert rc == 0
+        gpu_ctx.synchronize()
+        a = got.cpu().numpy()
+        for row in range(3):
+            ref = host[row].double().sum(0).numpy()
+            assert np.abs(a[row] - ref).max() / max(np.abs(ref).max(), 1e-30) <= 1e-5, f"call {call} sum {row}"
 
 
 def test_static_column_sums_reject_sizes_beyond_the_array():
