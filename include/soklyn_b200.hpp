@@ -282,34 +282,83 @@ struct InitGivenFunc : InitFunc { // hands back a prepared matrix (weights are l
         return values;
     }
 };
+// ChaCha with 8 rounds as rand_chacha::ChaCha8Rng runs it (src/util/function.rs:196-213 holds one per
+// initialiser): 64-bit block counter in words 12-13, stream id zero, the keystream read as little-endian
+// 32-bit words from block 0 on. seed_from_u64 is rand_core's: the eight key words are PCG32 (XSH-RR)
+// outputs, multiplier 6364136223846793005, increment 11634580027462260723, state advanced before each
+// output. Restated from the published algorithms; the crates' sources are not part of the reference tree.
+class ChaCha8Rng {
+  public:
+    static ChaCha8Rng seed_from_u64(uint64_t state) {
+        ChaCha8Rng r;
+        for (int i = 0; i < 8; ++i) {
+            state = state * 6364136223846793005ull + 11634580027462260723ull;
+            const uint32_t xorshifted = (uint32_t)(((state >> 18) ^ state) >> 27);
+            const uint32_t rot = (uint32_t)(state >> 59);
+            r.key_[i] = (xorshifted >> rot) | (xorshifted << ((32u - rot) & 31u));
+        }
+        return r;
+    }
+    uint32_t next_u32() {
+        if (index_ == 16) { block(); index_ = 0; }
+        return buf_[index_++];
+    }
+
+  private:
+    static uint32_t rotl(uint32_t x, int n) { return (x << n) | (x >> (32 - n)); }
+    static void quarter(uint32_t *s, int a, int b, int c, int d) {
+        s[a] += s[b]; s[d] = rotl(s[d] ^ s[a], 16);
+        s[c] += s[d]; s[b] = rotl(s[b] ^ s[c], 12);
+        s[a] += s[b]; s[d] = rotl(s[d] ^ s[a], 8);
+        s[c] += s[d]; s[b] = rotl(s[b] ^ s[c], 7);
+    }
+    void block() {
+        uint32_t in[16] = {0x61707865u, 0x3320646Eu, 0x79622D32u, 0x6B206574u};
+        for (int i = 0; i < 8; ++i) in[4 + i] = key_[i];
+        in[12] = (uint32_t)counter_; in[13] = (uint32_t)(counter_ >> 32); in[14] = 0; in[15] = 0;
+        uint32_t s[16];
+        for (int i = 0; i < 16; ++i) s[i] = in[i];
+        for (int r = 0; r < 4; ++r) {   // 8 rounds = 4 column + diagonal pairs
+            quarter(s, 0, 4, 8, 12); quarter(s, 1, 5, 9, 13); quarter(s, 2, 6, 10, 14); quarter(s, 3, 7, 11, 15);
+            quarter(s, 0, 5, 10, 15); quarter(s, 1, 6, 11, 12); quarter(s, 2, 7, 8, 13); quarter(s, 3, 4, 9, 14);
+        }
+        for (int i = 0; i < 16; ++i) buf_[i] = s[i] + in[i];
+        ++counter_;
+    }
+    uint32_t key_[8] = {0}, buf_[16] = {0};
+    uint64_t counter_ = 0;
+    int index_ = 16;
+};
+
+// normal_dist / uniform_dist of src/util/function.rs:219-248, in f32 arithmetic, operation for operation
+// (`u32::MAX as f32` is 2^32 after rounding, and so is `u32::MAX as f32 + 1.0`).
 class InitRandomBase : public InitFunc {
   public:
-    explicit InitRandomBase(uint64_t seed, float factor = 1.f) : state_(seed), factor_(factor) {}
+    explicit InitRandomBase(uint64_t seed, float factor = 1.f) : rng_(ChaCha8Rng::seed_from_u64(seed)), factor_(factor) {}
+    uint32_t next_u32() { return rng_.next_u32(); }
 
   protected:
-    uint32_t next_u32() {
-        uint64_t z = (state_ += 0x9E3779B97F4A7C15ull);
-        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
-        z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
-        return (uint32_t)((z ^ (z >> 31)) >> 32);
-    }
     std::vector<float> uniform(size_t n, float limit) {
         std::vector<float> v(n);
-        for (auto &x : v) x = factor_ * (-limit + ((float)next_u32() / 4294967295.0f) * (2.f * limit));
+        for (auto &x : v) {
+            const float raw = (float)next_u32() / 4294967296.0f;
+            x = factor_ * (-limit + raw * (2.0f * limit));
+        }
         return v;
     }
     std::vector<float> normal(size_t n, float std_dev) {
         std::vector<float> v(n);
         for (auto &x : v) {
             const float u1 = ((float)next_u32() + 1.0f) / 4294967296.0f;
-            const float u2 = (float)next_u32() / 4294967295.0f;
-            x = factor_ * std::sqrt(-2.0f * std::log(u1)) * std::cos(6.28318530717958647692f * u2) * std_dev;
+            const float u2 = (float)next_u32() / 4294967296.0f;
+            const float z = std::sqrt(-2.0f * std::log(u1)) * std::cos((2.0f * 3.14159274101257324219f) * u2);
+            x = factor_ * z * std_dev;
         }
         return v;
     }
 
   private:
-    uint64_t state_;
+    ChaCha8Rng rng_;
     float factor_;
 };
 struct InitXavierUniformFunc : InitRandomBase {

@@ -106,46 +106,51 @@ class LossFunc(Enum):
 
 
 class _InitBase:
-    """InitFunc (function.rs:190-319). The reference draws from rand_chacha's ChaCha8Rng,
-    whose source is not part of the reference tree; this mirror draws the same
-    distributions from numpy's PCG64 instead, so values differ from a reference run with
-    the same seed (load weights explicitly when bit-equal weights are needed)."""
+    """InitFunc (function.rs:190-319): ChaCha8Rng::seed_from_u64(seed), then normal_dist / uniform_dist
+    (function.rs:219-248) in f32 arithmetic, operation for operation. The generator is restated in
+    soklyn_b200/chacha.py from the published algorithms (the crates' sources are not part of the reference
+    tree): its block function is pinned by a known-answer vector, the seed expansion and the f32
+    transcendental functions (which follow the platform's libm in the reference) are not, so values can
+    differ from a reference run in the last bit. Load weights explicitly when bit-equal weights are needed."""
+
+    _TWO32 = np.float32(4294967296.0)   # `u32::MAX as f32`, and `u32::MAX as f32 + 1.0`, after rounding
 
     def __init__(self, seed: int, factor: float = 1.0):
-        self.rng = np.random.Generator(np.random.PCG64(seed))
+        from .chacha import ChaCha8Rng
+        self.rng = ChaCha8Rng.seed_from_u64(seed)
         self.factor = np.float32(factor)
 
     def _normal(self, total: int, std: float) -> np.ndarray:
-        # Box-Muller on two uniform draws, as normal_dist (function.rs:219-234)
-        u1 = (self.rng.integers(0, 2**32, total, dtype=np.uint64).astype(np.float32) + np.float32(1.0)) / np.float32(2**32)
-        u2 = self.rng.integers(0, 2**32, total, dtype=np.uint64).astype(np.float32) / np.float32(2**32 - 1)
-        z = np.sqrt(np.float32(-2.0) * np.log(u1)) * np.cos(np.float32(2.0 * math.pi) * u2)
-        return (self.factor * z * np.float32(std)).astype(np.float32)
+        draws = self.rng.next_u32s(2 * total)        # element i takes draws 2i (u1) and 2i + 1 (u2)
+        u1 = (draws[0::2].astype(np.float32) + np.float32(1.0)) / self._TWO32
+        u2 = draws[1::2].astype(np.float32) / self._TWO32
+        z = np.sqrt(np.float32(-2.0) * np.log(u1)) * np.cos((np.float32(2.0) * np.float32(math.pi)) * u2)
+        return ((self.factor * z) * np.float32(std)).astype(np.float32)
 
     def _uniform(self, total: int, limit: float) -> np.ndarray:
-        raw = self.rng.integers(0, 2**32, total, dtype=np.uint64).astype(np.float32) / np.float32(2**32 - 1)
+        raw = self.rng.next_u32s(total).astype(np.float32) / self._TWO32
         lim = np.float32(limit)
         return (self.factor * (-lim + raw * (np.float32(2.0) * lim))).astype(np.float32)
 
 
 class InitXavierUniformFunc(_InitBase):
     def init(self, fan_in: int, fan_out: int, length: int) -> np.ndarray:
-        return self._uniform(length, math.sqrt(6.0 / (fan_in + fan_out)))
+        return self._uniform(length, np.sqrt(np.float32(6.0) / np.float32(fan_in + fan_out)))
 
 
 class InitXavierNormalFunc(_InitBase):
     def init(self, fan_in: int, fan_out: int, length: int) -> np.ndarray:
-        return self._normal(length, math.sqrt(2.0 / (fan_in + fan_out)))
+        return self._normal(length, np.sqrt(np.float32(2.0) / np.float32(fan_in + fan_out)))
 
 
 class InitHeUniformFunc(_InitBase):
     def init(self, fan_in: int, fan_out: int, length: int) -> np.ndarray:
-        return self._uniform(length, math.sqrt(6.0 / fan_in))
+        return self._uniform(length, np.sqrt(np.float32(6.0) / np.float32(fan_in)))
 
 
 class InitHeNormalFunc(_InitBase):
     def init(self, fan_in: int, fan_out: int, length: int) -> np.ndarray:
-        return self._normal(length, math.sqrt(2.0 / fan_in))
+        return self._normal(length, np.sqrt(np.float32(2.0) / np.float32(fan_in)))
 
 
 class InitZeroFunc:

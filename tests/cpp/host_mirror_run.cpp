@@ -15,6 +15,7 @@
 //      f32 weights of every layer [K x N]; f32 x [batch x dims[0]]; f32 target [batch x dims[layers]].
 // OUT: a sequence of records {u32 name_len, name, u64 count, f32 values[count]}.
 #include <cstdio>
+#include <cstring>
 #include <fstream>
 #include <iostream>
 
@@ -281,7 +282,25 @@ int main(int argc, char **argv) {
     try {
         if (argc == 2 && std::string(argv[1]) == "checks") return host_checks();
         if (argc == 4 && std::string(argv[1]) == "train") return train(argv[2], argv[3]);
-        std::fprintf(stderr, "usage: %s checks | train IN OUT\n", argv[0]);
+        if (argc == 7 && std::string(argv[1]) == "draws") {
+            // draws KIND SEED FAN_IN FAN_OUT N: the initialiser's values as hexadecimal bit patterns, one per line,
+            // after the generator's first eight raw 32-bit draws
+            const std::string kind = argv[2];
+            const uint64_t seed = std::strtoull(argv[3], nullptr, 10);
+            const size_t fi = std::strtoull(argv[4], nullptr, 10), fo = std::strtoull(argv[5], nullptr, 10);
+            const size_t n = std::strtoull(argv[6], nullptr, 10);
+            InitXavierUniformFunc raw(seed);
+            for (int i = 0; i < 8; ++i) std::printf("%08x\n", raw.next_u32());
+            std::vector<float> v;
+            if (kind == "xavier_uniform") { InitXavierUniformFunc f(seed, 0.5f); v = f.init(fi, fo, n); }
+            else if (kind == "xavier_normal") { InitXavierNormalFunc f(seed); v = f.init(fi, fo, n); }
+            else if (kind == "he_uniform") { InitHeUniformFunc f(seed); v = f.init(fi, fo, n); }
+            else if (kind == "he_normal") { InitHeNormalFunc f(seed, 2.0f); v = f.init(fi, fo, n); }
+            else return 2;
+            for (float x : v) { uint32_t b; std::memcpy(&b, &x, 4); std::printf("%08x\n", b); }
+            return 0;
+        }
+        std::fprintf(stderr, "usage: %s checks | train IN OUT | draws KIND SEED FAN_IN FAN_OUT N\n", argv[0]);
         return 2;
     } catch (const std::exception &e) {
         std::fprintf(stderr, "error: %s\n", e.what());

@@ -93,6 +93,35 @@ def test_init_functions_have_the_reference_scales():
     assert (sk.InitZeroFunc().init(3, 3, 9) == 0).all()
 
 
+def test_chacha8_block_function_known_answers():
+    """The 8-round keystream of the all-zero key and nonce (the published ChaCha test vector for 8 rounds,
+    256-bit key), and for comparison the 20-round one; the generator reads the same stream word by word."""
+    from soklyn_b200.chacha import ChaCha8Rng, chacha_blocks
+    zero = np.zeros(8, np.uint32)
+    eight = chacha_blocks(zero, 0, 2, rounds=8)
+    assert eight[0].astype("<u4").tobytes().hex() == (
+        "3e00ef2f895f40d67f5bb8e81f09a5a12c840ec3ce9a7f3b181be188ef711a1e"
+        "984ce172b9216f419f445367456d5619314a42a3da86b001387bfdb80e0cfe42")
+    twenty = chacha_blocks(zero, 0, 1, rounds=20)
+    assert twenty[0].astype("<u4").tobytes().hex().startswith("76b8e0ada0f13d90405d6ae55386bd28bdd219b8a08ded1aa836efcc8b770dc7")
+    rng = ChaCha8Rng(zero)
+    a, b = rng.next_u32s(21), rng.next_u32s(11)          # reads that straddle block boundaries
+    assert np.array_equal(np.concatenate([a, b]), eight.reshape(-1))
+    assert ChaCha8Rng(zero).next_u32() == int(eight[0, 0])
+
+
+def test_seed_from_u64_is_deterministic_and_spreads_small_seeds():
+    from soklyn_b200.chacha import seed_words_from_u64
+    k0, k1 = seed_words_from_u64(0), seed_words_from_u64(1)
+    assert np.array_equal(k0, seed_words_from_u64(0)) and not np.array_equal(k0, k1)
+    assert len(set(k0.tolist())) == 8 and (k0 != 0).all()
+    a = sk.InitHeNormalFunc(5).init(64, 32, 100)
+    assert np.array_equal(a, sk.InitHeNormalFunc(5).init(64, 32, 100))
+    two = sk.InitHeNormalFunc(5)
+    first, second = two.init(64, 32, 60), two.init(64, 32, 40)      # the stream continues across calls
+    assert np.array_equal(np.concatenate([first, second]), a)
+
+
 def test_argmax_last_maximum_wins():
     from oracle import oracle as ok
     rows = np.array([[1, 3, 3, 0], [2, 2, 2, 2], [5, 1, 0, 0]], np.float32)
