@@ -163,6 +163,9 @@ def run_ours(args):
     spec = configs.CONFIGS[args.config]
     if args.batch:
         spec = configs.scaled(spec, batch=args.batch)
+    if args.lr > 0:
+        from dataclasses import replace
+        spec = replace(spec, lr=args.lr)
     ctx = sk.GpuContext(16, local_rank)
     if args.lean:
         ctx.set_lean_backward(True)
@@ -463,6 +466,7 @@ def main():
     ap.add_argument("--cpu-rows", type=int, default=256, help="rows of the batch the CPU baseline leg runs")
     ap.add_argument("--ref-rows", type=int, default=0,
                     help="rows of the batch the reference arm runs per step (0: the whole batch)")
+    ap.add_argument("--lr", type=float, default=0.0, help="override the configuration's learning rate")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gemm-sweep", action="store_true", help="leave the M = 16384 DenseBlock GEMM shapes out of the line")
     ap.add_argument("--lean", action="store_true", help="SK_OPTION_LEAN_BACKWARD (not the headline configuration)")

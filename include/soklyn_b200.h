@@ -129,7 +129,7 @@ uint64_t sk_launch_count(const sk_ctx *ctx);
  * bracketed by CUDA events on the context's stream; sk_profile_read waits for the stream and
  * returns launches and total milliseconds of one class since sk_profile_enable(ctx, 1). */
 enum { SK_PROF_GEMM_FORWARD = 0, SK_PROF_GEMM_DX = 1, SK_PROF_GEMM_DW = 2, SK_PROF_NORM = 3,
-       SK_PROF_OUTPUT_ERROR = 4, SK_PROF_COLSUM = 5, SK_PROF_UPDATE = 6, SK_PROF_CLASSES = 7 };
+       SK_PROF_OUTPUT_ERROR = 4, SK_PROF_COLSUM = 5, SK_PROF_UPDATE = 6, SK_PROF_EXCHANGE = 7, SK_PROF_CLASSES = 8 };
 int sk_profile_enable(sk_ctx *ctx, int on);
 int sk_profile_read(sk_ctx *ctx, uint32_t kernel_class, uint64_t *launches, double *total_ms);
 
@@ -230,16 +230,19 @@ int sk_reduce_update_broadcast(sk_ctx *ctx, const sk_dense *layer, void *const *
  * count actually used for a shape: the largest <= blocks that splits evenly; 0 = the shape cannot be
  * split); inside a block rank r owns rows [r*K/(blocks*world), (r+1)*K/(blocks*world)) and keeps f32
  * masters and moments current for those rows only. Per block: the dW GEMM writes the block of the local
- * 16-bit gradient, one kernel on a second stream (on SMs the GEMMs leave free) pulls the owned rows from
- * every rank, adds them, steps them and stores the new 16-bit rows into every rank's weight tensor, and the
- * dX GEMM of the layer below waits, inside its TMA producer, only for the blocks of rows its tile needs.
- * The last block's kernel also adds the [3 x N] column sums of all ranks and steps bias and normalisation
- * parameters. All waits are bounded (SK_ERR_DEVICE_TIMEOUT at the next sk_sync; a kernel whose wait gave up
- * changes no weight). Per layer the caller provides, for every rank as mapped into this process: the gradient
- * buffer T [K x N], the weight tensor T [K x N] (this rank's entry must be the block's `w`), sk_dp_flag_bytes()
- * bytes of flag words (zero at set-up), and a column-sum buffer f32 [3 x N]. `epoch` must grow by one per call.
- * 16-bit blocks without BatchNorm; world = 2, 4 or 8. When the call returns, later work on the context's
- * stream is ordered after the whole exchange. */
+ * 16-bit gradient; a kernel on a second stream (on SMs the GEMMs leave free) pulls the owned rows from
+ * every rank and adds them; the optimiser step of those rows runs on the context's stream; a second kernel
+ * on the second stream stores the new 16-bit rows into every other rank's weight tensor; and the dX GEMM of
+ * the layer below waits, inside its TMA producer, only for the blocks of rows its tile needs. The last
+ * block's reduction also adds the [3 x N] column sums of all ranks for the bias / normalisation-parameter
+ * step. Work of one GPU is ordered by streams and events; kernels wait only for flags raised by OTHER GPUs,
+ * and every such wait is bounded (SK_ERR_DEVICE_TIMEOUT at the next sk_sync; after a wait gave up no weight
+ * is changed and no flag raised). Per layer the caller provides, for every rank as mapped into this
+ * process: the gradient buffer T [K x N], the weight tensor T [K x N] (this rank's entry must be the
+ * block's `w`), sk_dp_flag_bytes() bytes of flag words (zero at set-up), and a column-sum buffer f32
+ * [3 x N]; plus local scratch of at least sk_dp_scratch_bytes(K, N, world) bytes for the largest layer
+ * (256-byte aligned). `epoch` must grow by one per call. 16-bit blocks without BatchNorm; world = 2, 4 or
+ * 8. When the call returns, later work on the context's stream is ordered after the whole exchange. */
 typedef struct {
     void *const *peer_grad;
     void *const *peer_w;
@@ -248,11 +251,13 @@ typedef struct {
 } sk_exchange;
 uint32_t sk_dp_blocks(uint32_t K, uint32_t N, uint32_t world, uint32_t blocks);
 uint32_t sk_dp_flag_bytes(void);
+size_t sk_dp_scratch_bytes(uint32_t K, uint32_t N, uint32_t world);
 int sk_dp_backward(sk_ctx *ctx, const sk_dense *const *layers, const sk_exchange *exchange, uint32_t n_layers,
                    const void *target, uint32_t target_rows, const void *x, uint32_t x_rows, uint32_t loss,
                    uint32_t loss_act, float loss_leaky, const sk_optim *linear, const sk_optim *norm_opt,
                    uint32_t batch, uint32_t batch_stat, uint32_t world, uint32_t rank, uint32_t blocks,
-                   uint32_t epoch, float learn_rate, float grad_clamp, uint32_t step);
+                   uint32_t epoch, float learn_rate, float grad_clamp, uint32_t step, float *scratch,
+                   size_t scratch_bytes);
 
 /* Exchange arena of one rank: sk_peer_alloc allocates `bytes` of zeroed device memory (set-up time,
  * not the hot path) and returns a 64-byte CUDA IPC handle for it; the other ranks (other processes

@@ -137,7 +137,8 @@ _SIGS = {
     "sk_dp_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p,
                                  C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, C.c_void_p, C.c_void_p, C.c_uint32,
                                  C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, C.c_float,
-                                 C.c_uint32]),
+                                 C.c_uint32, C.c_void_p, C.c_size_t]),
+    "sk_dp_scratch_bytes": (C.c_size_t, [C.c_uint32, C.c_uint32, C.c_uint32]),
     "sk_copy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
     "sk_peer_alloc": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p]),
     "sk_peer_open": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p)]),

@@ -44,6 +44,7 @@ struct sk_ctx {
     cudaStream_t comm_stream = nullptr;    // exchange kernels run here, beside the GEMMs
     cudaEvent_t comm_done = nullptr;
     uint32_t *dp_counters = nullptr;       // one completion counter per (layer, block), zero between launches
+    std::vector<cudaEvent_t> dp_events;    // per block: dW written / reduced / stepped
     uint32_t dp_reserve_override = 0;      // SK_DP_RESERVE_SMS at context creation (0: by rank count)
     // Column sums handed from the dX epilogue to the weight update of the same layer. Only inside
     // sk_ffn_backward (nothing can touch the tensors or the workspace in between there).
@@ -360,6 +361,7 @@ int hidden_error_impl(sk_ctx *c, const sk_dense *cur, const sk_dense *next, uint
     epi.d_prenorm_lp = f32 ? nullptr : (T *)cur->d_prenorm_lp;
     epi.N = cur->N; epi.norm = cur->norm; epi.act = cur->act; epi.leaky = cur->leaky_coeff;
     epi.inv_n = 1.0f / (float)cur->N; epi.inv_m = 1.0f / (float)batch_stat; epi.vec_ok = layer_vec_ok(cur);
+    epi.acc_scale = f32 ? 1.0f : kLpScaleInv;
     const uint32_t ec = next->N;
     const T *dy = f32 ? (const T *)next->d_prenorm : (const T *)next->d_prenorm_lp;
     const T *wn = f32 ? (const T *)master_of<T>(next->master_w, next->w) : (const T *)next->w;
@@ -457,9 +459,10 @@ VectorParams<T> vector_params(const sk_dense *L, const Optim &lin, const Optim &
 
 template <typename T>
 int vector_update_launch(sk_ctx *c, const sk_dense *L, const float *partial, uint32_t nblocks, const Optim &lin,
-                         const Optim &nrm, const Hyper &hyp) {
+                         const Optim &nrm, const Hyper &hyp, const int *abort_flag = nullptr) {
     ProfScope ps(c, SK_PROF_UPDATE);
-    vector_update_kernel<T><<<(L->N + 127) / 128, 128, 0, c->stream>>>(partial, nblocks, L->N, vector_params<T>(L, lin, nrm, hyp));
+    vector_update_kernel<T><<<(L->N + 127) / 128, 128, 0, c->stream>>>(partial, nblocks, L->N, vector_params<T>(L, lin, nrm, hyp),
+                                                                         abort_flag);
     c->launches++;
     return check_cuda(c, cudaGetLastError(), "bias / norm parameter step");
 }
@@ -496,6 +499,7 @@ int backward_update_impl(sk_ctx *c, const sk_dense *L, const void *x, uint32_t b
     EpiWeightUpdate<T> epi{};
     epi.w = (T *)L->w; epi.master = master_of<T>(L->master_w, L->w); epi.dv = L->dv_w; epi.dm = L->dm_w;
     epi.N = L->N; epi.opt = lin; epi.hyp = hyp;
+    epi.gscale = f32 ? kLossScaleInv : kLossScaleInv * kLpScaleInv;
     epi.vec_ok = L->N % 8 == 0 && aligned16(L->w) && aligned16(epi.master) && aligned16(L->dv_w) && aligned16(L->dm_w);
     ProfScope ps(c, SK_PROF_GEMM_DW);
     if (f32) {
@@ -524,7 +528,7 @@ int backward_grads_impl(sk_ctx *c, const sk_dense *L, const void *x, uint32_t ba
     colsum_final_kernel<<<(3 * L->N + 255) / 256, 256, 0, c->stream>>>((const float *)c->workspace, colsums, L->N, nblocks);
     c->launches++;
     if ((rc = check_cuda(c, cudaGetLastError(), "column sums (final)"))) return rc;
-    EpiStoreF32 epi{dw, L->N, L->N % 8 == 0 && aligned16(dw)};
+    EpiStoreF32 epi{dw, L->N, L->dtype == SK_F32 ? 1.0f : kLpScaleInv, L->N % 8 == 0 && aligned16(dw)};
     ProfScope ps(c, SK_PROF_GEMM_DW);
     if (L->dtype == SK_F32)
         rc = check_cuda(c, run_gemm<T, float, false, true>(c, L->dtype, (const T *)x, L->K, L->d_prenorm,
@@ -549,7 +553,7 @@ int backward_grads_lp_impl(sk_ctx *c, const sk_dense *L, const void *x, uint32_t
     colsum_final_kernel<<<(3 * L->N + 255) / 256, 256, 0, c->stream>>>(slabs, colsums, L->N, nblocks);
     c->launches++;
     if ((rc = check_cuda(c, cudaGetLastError(), "column sums (final)"))) return rc;
-    EpiStoreScaled<T> epi{(T *)g, L->N, 1.0f / (float)batch_stat, L->N % 8 == 0 && aligned16(g)};
+    EpiStoreScaled<T> epi{(T *)g, L->N, (L->dtype == SK_F32 ? 1.0f : kLpScaleInv) / (float)batch_stat, L->N % 8 == 0 && aligned16(g)};
     ProfScope ps(c, SK_PROF_GEMM_DW);
     if (L->dtype == SK_F32)
         rc = check_cuda(c, run_gemm<T, float, false, true>(c, L->dtype, (const T *)x, L->K, L->d_prenorm,
@@ -649,7 +653,7 @@ template <typename T>
 int dw_rows_lp(sk_ctx *c, const sk_dense *L, const void *x, uint32_t batch, uint32_t batch_stat, void *g, uint32_t row0,
                uint32_t nrows) {
     T *out = (T *)g + (size_t)row0 * L->N;
-    EpiStoreScaled<T> epi{out, L->N, 1.0f / (float)batch_stat, L->N % 8 == 0 && aligned16(out)};
+    EpiStoreScaled<T> epi{out, L->N, kLpScaleInv / (float)batch_stat, L->N % 8 == 0 && aligned16(out)};
     ProfScope ps(c, SK_PROF_GEMM_DW);
     int rc = check_cuda(c, run_gemm<T, T, false, true>(c, L->dtype, (const T *)x + row0, L->K, (const T *)L->d_prenorm_lp,
                                                         L->N, nrows, L->N, batch, epi), "weight gradient gemm (row block)");
@@ -657,26 +661,61 @@ int dw_rows_lp(sk_ctx *c, const sk_dense *L, const void *x, uint32_t batch, uint
     return rc;
 }
 
-template <typename T, int W>
-cudaError_t launch_exchange(sk_ctx *c, const ExchangeArgs<T> &a, uint32_t ctas) {
-    static uint64_t attr_set[4] = {0, 0, 0, 0};
-    constexpr int kSmem = 120 * 1024;   // more than half an SM's shared memory: one block per SM, none beside a GEMM block
-    auto kernel = exchange_chunk_kernel<T, W>;
+constexpr int kExchangeSmem = 120 * 1024;   // more than half an SM's shared memory: one block per SM, none beside a GEMM block
+
+template <class Kernel> cudaError_t exclusive_smem_attr(sk_ctx *c, Kernel kernel, uint64_t (&attr_set)[4]) {
     const unsigned dev = (unsigned)c->device & 255u;
-    if (!(attr_set[dev >> 6] >> (dev & 63) & 1ull)) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-        if (e != cudaSuccess) return e;
-        attr_set[dev >> 6] |= 1ull << (dev & 63);
-    }
-    kernel<<<ctas, kExchangeThreads, kSmem, c->comm_stream>>>(a);
+    if (attr_set[dev >> 6] >> (dev & 63) & 1ull) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kExchangeSmem);
+    if (e == cudaSuccess) attr_set[dev >> 6] |= 1ull << (dev & 63);
+    return e;
+}
+
+template <typename T, int W> cudaError_t launch_reduce(sk_ctx *c, const ReduceArgs &a, uint32_t ctas) {
+    static uint64_t attr_set[4] = {0, 0, 0, 0};
+    cudaError_t e = exclusive_smem_attr(c, reduce_rows_kernel<T, W>, attr_set);
+    if (e != cudaSuccess) return e;
+    reduce_rows_kernel<T, W><<<ctas, kExchangeThreads, kExchangeSmem, c->comm_stream>>>(a);
     return cudaGetLastError();
+}
+template <typename T, int W> cudaError_t launch_spread(sk_ctx *c, const SpreadArgs &a, uint32_t ctas) {
+    static uint64_t attr_set[4] = {0, 0, 0, 0};
+    cudaError_t e = exclusive_smem_attr(c, spread_rows_kernel<T, W>, attr_set);
+    if (e != cudaSuccess) return e;
+    spread_rows_kernel<T, W><<<ctas, kExchangeThreads, kExchangeSmem, c->comm_stream>>>(a);
+    return cudaGetLastError();
+}
+template <typename T> cudaError_t launch_reduce_w(sk_ctx *c, uint32_t world, const ReduceArgs &a, uint32_t ctas) {
+    switch (world) {
+    case 2: return launch_reduce<T, 2>(c, a, ctas);
+    case 4: return launch_reduce<T, 4>(c, a, ctas);
+    case 8: return launch_reduce<T, 8>(c, a, ctas);
+    default: return cudaErrorInvalidValue;
+    }
+}
+template <typename T> cudaError_t launch_spread_w(sk_ctx *c, uint32_t world, const SpreadArgs &a, uint32_t ctas) {
+    switch (world) {
+    case 2: return launch_spread<T, 2>(c, a, ctas);
+    case 4: return launch_spread<T, 4>(c, a, ctas);
+    case 8: return launch_spread<T, 8>(c, a, ctas);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+// Event `kind` (0: block of dW written, 1: block reduced, 2: block stepped) of block `ch`; created on first use.
+cudaEvent_t dp_event(sk_ctx *c, uint32_t ch, uint32_t kind) {
+    const size_t idx = (size_t)ch * 3 + kind;
+    if (c->dp_events.size() <= idx) c->dp_events.resize(idx + 1, nullptr);
+    if (!c->dp_events[idx]) cudaEventCreateWithFlags(&c->dp_events[idx], cudaEventDisableTiming);
+    return c->dp_events[idx];
 }
 
 template <typename T>
 int dp_backward_impl(sk_ctx *c, const sk_dense *const *layers, const sk_exchange *ex, uint32_t n, const void *target,
                      uint32_t target_rows, const void *x, uint32_t x_rows, uint32_t loss, uint32_t loss_act,
                      float loss_leaky, const sk_optim *lin_, const sk_optim *nrm_, uint32_t batch, uint32_t batch_stat,
-                     uint32_t world, uint32_t rank, uint32_t chunks, uint32_t epoch, float lr, float clamp, uint32_t step) {
+                     uint32_t world, uint32_t rank, uint32_t chunks, uint32_t epoch, float lr, float clamp, uint32_t step,
+                     float *scratch) {
     const uint32_t last = n - 1;
     uint32_t reserve = c->dp_reserve_override ? c->dp_reserve_override : (world <= 2 ? 8u : world <= 4 ? 16u : 20u);
     if (reserve >= (uint32_t)c->num_sms) reserve = (uint32_t)c->num_sms / 4;
@@ -691,13 +730,14 @@ int dp_backward_impl(sk_ctx *c, const sk_dense *const *layers, const sk_exchange
         const uint32_t in_rows = ii == 0 ? x_rows : layers[ii - 1]->max_batch;
         if ((rc = check_batch(c, L, in_rows, batch))) break;
         if (ii < last) {
-            // delta of this layer from the next layer's weights: its rows arrive block by block
+            // delta of this layer from the next layer's weights: the other ranks' rows arrive block by block,
+            // this rank's own rows were stepped earlier on this stream
             const sk_dense *nx = layers[ii + 1];
             const uint32_t *flags_b = reinterpret_cast<const uint32_t *>(ex[ii + 1].peer_flags[rank]) + kMaxChunks * kMaxRanks;
-            TcGate gate{flags_b, world, (uint32_t)kMaxRanks, p_next, nx->K / p_next, epoch};
+            TcGate gate{flags_b, world, rank, (uint32_t)kMaxRanks, p_next, nx->K / p_next, epoch};
             const bool gated = tc_eligible(c, L->dtype, nx->d_prenorm_lp, nx->N, nx->w, nx->N);
             if (!gated) {
-                wait_words_kernel<<<1, 64, 0, c->stream>>>(flags_b, p_next, kMaxRanks, world, epoch, c->tc_err);
+                wait_words_kernel<<<1, 64, 0, c->stream>>>(flags_b, p_next, kMaxRanks, world, rank, epoch, c->tc_err);
                 c->launches++; c->tc_launches++;
             }
             c->in_ffn_backward = true;
@@ -705,7 +745,7 @@ int dp_backward_impl(sk_ctx *c, const sk_dense *const *layers, const sk_exchange
             c->in_ffn_backward = false;
             if (rc) break;
         }
-        // column sums of this rank's rows into its arena (the other ranks read them in the last block's kernel)
+        // column sums of this rank's rows into its arena (the other ranks read them in the last block's reduction)
         uint32_t nslabs = 0;
         const float *slabs = column_sum_slabs(c, L, batch, &nslabs, &rc);
         if (rc) break;
@@ -715,49 +755,82 @@ int dp_backward_impl(sk_ctx *c, const sk_dense *const *layers, const sk_exchange
 
         const uint32_t P = dp_chunks_for(L->K, L->N, world, chunks);
         const uint32_t rows_block = L->K / P, rows_own = rows_block / world;
+        const size_t own_len = (size_t)rows_own * L->N;
         const Optim lin = make_optim(&lin_[ii], step), nrm = make_optim(&nrm_[ii], step);
-        ExchangeArgs<T> a{};
+        const Hyper hyp_w{lr, clamp, 1.0f, L->regu, L->regu_coeff};   // the staged gradients are already averaged
+        float *colsum_total = scratch;                                 // [3 x N], then the summed rows of every block
+        float *gsum = scratch + (((size_t)3 * L->N + 63) / 64) * 64;
+        ReduceArgs ra{};
+        SpreadArgs sa{};
         PeerPtrs pf{};
         for (uint32_t r = 0; r < world; ++r) {
-            a.grad.p[r] = E.peer_grad[r]; a.w.p[r] = E.peer_w[r]; a.flags.p[r] = E.peer_flags[r]; a.colsums.p[r] = E.peer_colsums[r];
+            ra.grad.p[r] = E.peer_grad[r]; ra.flags.p[r] = E.peer_flags[r]; ra.colsums.p[r] = E.peer_colsums[r];
+            sa.w.p[r] = E.peer_w[r]; sa.flags.p[r] = E.peer_flags[r];
             pf.p[r] = E.peer_flags[r];
         }
-        a.world = world; a.rank = rank; a.epoch = epoch;
-        a.master = master_of<T>(L->master_w, L->w); a.dv = L->dv_w; a.dm = L->dm_w;
-        a.opt = lin; a.hyp = Hyper{lr, clamp, 1.0f, L->regu, L->regu_coeff};
-        a.err = c->tc_err; a.N = L->N;
-        a.vp = vector_params<T>(L, lin, nrm, Hyper{lr, clamp, 1.0f / (float)batch_stat, L->regu, L->regu_coeff});
+        ra.world = sa.world = world; ra.rank = sa.rank = rank; ra.epoch = sa.epoch = epoch;
+        ra.err = c->tc_err; sa.err = c->tc_err; ra.N = L->N; ra.colsum_total = colsum_total;
+        T *w = (T *)L->w;
+        float *master = master_of<T>(L->master_w, L->w);
+        auto own_off = [&](uint32_t ch) { return ((size_t)ch * rows_block + (size_t)rank * rows_own) * L->N; };
+        // the optimiser step of block `ch` (main stream, every SM) and its all-gather (second stream)
+        auto step_and_spread = [&](uint32_t ch) -> int {
+            const size_t off = own_off(ch);
+            cudaStreamWaitEvent(c->stream, dp_event(c, ch, 1), 0);
+            const bool vec = own_len % 8 == 0 && aligned16(gsum) && aligned16(w + off) && aligned16(master + off);
+            size_t blocks = (own_len / 8 + kRowThreads - 1) / kRowThreads;
+            const size_t cap = (size_t)c->num_sms * 8;
+            if (blocks > cap) blocks = cap;
+            if (blocks < 1) blocks = 1;
+            {
+                ProfScope ps(c, SK_PROF_UPDATE);
+                weight_update_range_kernel<T, float><<<(uint32_t)blocks, kRowThreads, 0, c->stream>>>(
+                    gsum + (size_t)ch * own_len, kLossScaleInv, w + off, master + off, L->dv_w + off, L->dm_w + off, own_len, lin,
+                    hyp_w, vec, c->tc_err);
+            }
+            c->launches++;
+            cudaEventRecord(dp_event(c, ch, 2), c->stream);
+            cudaStreamWaitEvent(c->comm_stream, dp_event(c, ch, 2), 0);
+            sa.chunk = ch; sa.off = off; sa.len = own_len; sa.done = c->dp_counters + ii * kMaxChunks + ch;
+            ProfScope ps(c, SK_PROF_EXCHANGE, c->comm_stream);
+            const cudaError_t e = launch_spread_w<T>(c, world, sa, reserve);
+            c->launches++;
+            return check_cuda(c, e, "all-gather kernel");
+        };
         for (uint32_t ch = 0; ch < P && rc == SK_OK; ++ch) {
             if ((rc = dw_rows_lp<T>(c, L, in, batch, batch_stat, E.peer_grad[rank], ch * rows_block, rows_block))) break;
-            signal_chunk_kernel<<<1, 32, 0, c->stream>>>(pf, world, (0 * kMaxChunks + ch) * kMaxRanks + rank, epoch);
+            signal_chunk_kernel<<<1, 32, 0, c->stream>>>(pf, world, rank, (0 * kMaxChunks + ch) * kMaxRanks + rank, epoch);
             c->launches++;
-            a.chunk = ch;
-            a.off = ((size_t)ch * rows_block + (size_t)rank * rows_own) * L->N;
-            a.len = (size_t)rows_own * L->N;
-            a.done = c->dp_counters + ii * kMaxChunks + ch;
-            a.do_vector = ch == P - 1;
-            ProfScope ps(c, SK_PROF_UPDATE, c->comm_stream);
-            cudaError_t e;
-            switch (world) {
-            case 2: e = launch_exchange<T, 2>(c, a, reserve); break;
-            case 4: e = launch_exchange<T, 4>(c, a, reserve); break;
-            case 8: e = launch_exchange<T, 8>(c, a, reserve); break;
-            default: e = cudaErrorInvalidValue;
+            cudaEventRecord(dp_event(c, ch, 0), c->stream);
+            cudaStreamWaitEvent(c->comm_stream, dp_event(c, ch, 0), 0);
+            ra.chunk = ch; ra.off = own_off(ch); ra.len = own_len; ra.sum = gsum + (size_t)ch * own_len;
+            ra.do_colsums = ch == P - 1;
+            {
+                ProfScope ps(c, SK_PROF_EXCHANGE, c->comm_stream);
+                const cudaError_t e = launch_reduce_w<T>(c, world, ra, reserve);
+                c->launches++; c->tc_launches++;
+                if ((rc = check_cuda(c, e, "reduce-scatter kernel"))) break;
             }
-            c->launches++; c->tc_launches++;
-            rc = check_cuda(c, e, "exchange kernel");
+            cudaEventRecord(dp_event(c, ch, 1), c->comm_stream);
+            if (ch >= 1 && (rc = step_and_spread(ch - 1))) break;
         }
+        if (rc == SK_OK) rc = step_and_spread(P - 1);
+        if (rc) break;
+        // bias and normalisation parameters from the column sums of all ranks (summed by the last block's reduction,
+        // which the wait for that block's event above has ordered before this)
+        const Hyper hyp_v{lr, clamp, 1.0f / (float)batch_stat, L->regu, L->regu_coeff};
+        rc = vector_update_launch<T>(c, L, colsum_total, 1, lin, nrm, hyp_v, c->tc_err);
         p_next = P;
     }
     c->fused_colsum_key = nullptr;
     c->reserve_sms = saved_reserve;
     if (rc) return rc;
-    // the step is complete when this rank's exchange kernels have finished and every rank's rows of the
+    // the step is complete when this rank's exchange kernels have finished and every other rank's rows of the
     // first layer have landed here (the deltas above already waited for the other layers' rows)
     cudaEventRecord(c->comm_done, c->comm_stream);
     cudaStreamWaitEvent(c->stream, c->comm_done, 0);
     const uint32_t *flags_b0 = reinterpret_cast<const uint32_t *>(ex[0].peer_flags[rank]) + kMaxChunks * kMaxRanks;
-    wait_words_kernel<<<1, 64, 0, c->stream>>>(flags_b0, p_next, kMaxRanks, world, epoch, c->tc_err);
+    wait_words_kernel<<<1, 64, 0, c->stream>>>(flags_b0, p_next, kMaxRanks, world, rank, epoch, c->tc_err);
     c->launches++; c->tc_launches++;
     return check_cuda(c, cudaGetLastError(), "end of the data-parallel backward pass");
 }
@@ -831,6 +904,7 @@ void sk_ctx_destroy(sk_ctx *c) {
     if (c->dp_counters) cudaFree(c->dp_counters);
     if (c->comm_stream) { cudaStreamSynchronize(c->comm_stream); cudaStreamDestroy(c->comm_stream); }
     if (c->comm_done) cudaEventDestroy(c->comm_done);
+    for (cudaEvent_t e : c->dp_events) if (e) cudaEventDestroy(e);
     for (cudaEvent_t e : c->ev_pool) cudaEventDestroy(e);
     if (c->own_stream) cudaStreamDestroy(c->stream);
     delete c;
@@ -1149,11 +1223,18 @@ uint32_t sk_dp_blocks(uint32_t K, uint32_t N, uint32_t world, uint32_t wanted) {
 
 uint32_t sk_dp_flag_bytes(void) { return (uint32_t)(kFlagWordsPerLayer * sizeof(uint32_t)); }
 
+size_t sk_dp_scratch_bytes(uint32_t K, uint32_t N, uint32_t world) {
+    if (world == 0) return 0;
+    return ((((size_t)3 * N + 63) / 64) * 64 + (size_t)(K / world) * N) * sizeof(float);
+}
+
 int sk_dp_backward(sk_ctx *c, const sk_dense *const *layers, const sk_exchange *ex, uint32_t n, const void *target,
                    uint32_t target_rows, const void *x, uint32_t x_rows, uint32_t loss, uint32_t loss_act, float loss_leaky,
                    const sk_optim *lin, const sk_optim *nrm, uint32_t batch, uint32_t batch_stat, uint32_t world,
-                   uint32_t rank, uint32_t blocks, uint32_t epoch, float lr, float clamp, uint32_t step) {
-    if (!c || !layers || !ex || !lin || !nrm || !target || !x) return SK_ERR_NULL_POINTER;
+                   uint32_t rank, uint32_t blocks, uint32_t epoch, float lr, float clamp, uint32_t step, float *scratch,
+                   size_t scratch_bytes) {
+    if (!c || !layers || !ex || !lin || !nrm || !target || !x || !scratch) return SK_ERR_NULL_POINTER;
+    if (reinterpret_cast<uintptr_t>(scratch) % 256 != 0) return fail(c, SK_ERR_NULL_POINTER, "scratch must be 256-byte aligned");
     if (n == 0 || n > kDpMaxLayers) return fail(c, SK_ERR_INVALID_CONFIGURATION, "1 to %u layers", kDpMaxLayers);
     if (!(world == 2 || world == 4 || world == 8) || rank >= world)
         return fail(c, SK_ERR_INVALID_CONFIGURATION, "rank %u of %u ranks (2, 4 or 8)", rank, world);
@@ -1181,6 +1262,9 @@ int sk_dp_backward(sk_ctx *c, const sk_dense *const *layers, const sk_exchange *
                 reinterpret_cast<uintptr_t>(ex[i].peer_colsums[r]) % 16)
                 return fail(c, SK_ERR_NULL_POINTER, "exchange pointer of layer %u, rank %u is NULL or unaligned", i, r);
         if (ex[i].peer_w[rank] != L->w) return fail(c, SK_ERR_INVALID_CONFIGURATION, "layer %u: the weight tensor must be this rank's entry of peer_w", i);
+        if (sk_dp_scratch_bytes(L->K, L->N, world) > scratch_bytes)
+            return fail(c, SK_ERR_WORKSPACE, "layer %u needs %zu bytes of exchange scratch, %zu given", i,
+                        sk_dp_scratch_bytes(L->K, L->N, world), scratch_bytes);
     }
     if (cudaSetDevice(c->device) != cudaSuccess) return fail(c, SK_ERR_DRIVER, "cannot select device %d", c->device);
     if (!c->comm_stream) {
@@ -1193,9 +1277,9 @@ int sk_dp_backward(sk_ctx *c, const sk_dense *const *layers, const sk_exchange *
     c->fused_colsum_key = nullptr;
     return layers[0]->dtype == SK_F16
                ? dp_backward_impl<__half>(c, layers, ex, n, target, target_rows, x, x_rows, loss, loss_act, loss_leaky, lin, nrm,
-                                          batch, batch_stat, world, rank, blocks, epoch, lr, clamp, step)
+                                          batch, batch_stat, world, rank, blocks, epoch, lr, clamp, step, scratch)
                : dp_backward_impl<__nv_bfloat16>(c, layers, ex, n, target, target_rows, x, x_rows, loss, loss_act, loss_leaky,
-                                                 lin, nrm, batch, batch_stat, world, rank, blocks, epoch, lr, clamp, step);
+                                                 lin, nrm, batch, batch_stat, world, rank, blocks, epoch, lr, clamp, step, scratch);
 }
 
 int sk_peer_alloc(sk_ctx *c, size_t bytes, void **ptr, unsigned char handle_out[64]) {

@@ -13,6 +13,13 @@ namespace sk {
 
 constexpr float kLossScale = 512.0f;          // ffn/backward.cu:8
 constexpr float kLossScaleInv = 1.0f / 512.0f;
+// The 16-bit copy of d_prenorm that feeds the tensor-core GEMMs (d_prenorm_lp) holds d_prenorm * kLpScale,
+// i.e. the delta at an effective loss scale of 32 instead of 512. The reference keeps d_prenorm in f32
+// (src/mlp.rs:273-276), where the factor 512 costs nothing; in f16 it overflows (|delta| * 512 > 65504 from
+// |delta| = 128 on, which the wide network reaches at its first step), and infinities in dY poison dW and
+// every delta below. A power of two, so the copy loses no precision; the consumers multiply it back.
+constexpr float kLpScale = 1.0f / 16.0f;
+constexpr float kLpScaleInv = 16.0f;
 
 // ---- storage types -------------------------------------------------------------------
 __device__ __forceinline__ float to_f32(float v) { return v; }

@@ -46,15 +46,6 @@ __device__ __forceinline__ void store_run(T *p, bool vec, const float (&in)[V]) 
     }
 }
 
-// f32 run stored with the evict-first hint: tensors that are written once and not read again by
-// the kernels that follow, so that they do not push operands of the running GEMM out of L2.
-template <int V>
-__device__ __forceinline__ void store_run_streaming(float *p, const float (&in)[V]) {
-    static_assert(V % 4 == 0, "whole 128-bit stores");
-#pragma unroll
-    for (int i = 0; i < V; i += 4) __stcs(reinterpret_cast<float4 *>(p + i), make_float4(in[i], in[i + 1], in[i + 2], in[i + 3]));
-}
-
 // Raw (unconverted) run of V elements, for loads issued ahead of their use.
 template <typename T, int V> __device__ __forceinline__ Pack<T, V> load_pack(const T *p) {
     return *reinterpret_cast<const Pack<T, V> *>(p);
@@ -181,6 +172,9 @@ template <typename T, int ACT = -1, int NORM = -1> struct EpiHidden {
     // d_prenorm, d_norm_w or d_norm_b again (the GEMMs read d_prenorm_lp), so their stores are skipped.
     // Only set together with colsum_partial.
     uint32_t lean;
+    // Factor that brings the accumulators back to the scale of the reference's dY (the 16-bit copy of the
+    // next layer's d_prenorm is stored scaled down by kLpScale): 1 in f32, 1 / kLpScale in 16-bit modes.
+    float acc_scale;
     struct Acc { float dp[8], gw[8], gb[8]; };
 
     __device__ __forceinline__ uint32_t A() const { return ACT >= 0 ? (uint32_t)ACT : act; }
@@ -189,7 +183,7 @@ template <typename T, int ACT = -1, int NORM = -1> struct EpiHidden {
     __device__ __forceinline__ void one(uint32_t row, uint32_t col, float s) const {
         const size_t idx = (size_t)row * N + col;
         const float delta = to_f32(mask[idx]) *
-                            activation_derivative(act, s, to_f32(predrop[idx]), to_f32(preact[idx]), leaky);
+                            activation_derivative(act, s * acc_scale, to_f32(predrop[idx]), to_f32(preact[idx]), leaky);
         grad[idx] = delta;
         const float r = norm ? to_f32(rstd[norm == 3 ? col : row]) : 0.0f;
         const float pv = norm == 1 ? to_f32(prenorm[idx]) : 0.0f;
@@ -198,7 +192,7 @@ template <typename T, int ACT = -1, int NORM = -1> struct EpiHidden {
         d_prenorm[idx] = g.d_prenorm;
         d_norm_w[idx] = g.d_norm_w;
         d_norm_b[idx] = g.d_norm_b;
-        if (d_prenorm_lp) d_prenorm_lp[idx] = from_f32<T>(g.d_prenorm);
+        if (d_prenorm_lp) d_prenorm_lp[idx] = from_f32<T>(g.d_prenorm * kLpScale);
     }
 
     // vector path on unpacked inputs of one run. nw: normalisation weights of the columns,
@@ -210,7 +204,7 @@ template <typename T, int ACT = -1, int NORM = -1> struct EpiHidden {
         const size_t idx = (size_t)row * N + col0;
         float gr[V], dp[V], gw[V], gb[V];
 #pragma unroll
-        for (int j = 0; j < V; ++j) gr[j] = acc[j];
+        for (int j = 0; j < V; ++j) gr[j] = acc[j] * acc_scale;
         activation_derivative_v<kFastMath<T>, V>(A(), gr, pd, pa, leaky);
 #pragma unroll
         for (int j = 0; j < V; ++j) gr[j] *= mk[j];
@@ -236,19 +230,17 @@ template <typename T, int ACT = -1, int NORM = -1> struct EpiHidden {
             }
         }
         if (!lean) {
-            if constexpr (V % 4 == 0) {
-                store_run_streaming<V>(grad + idx, gr);
-                store_run_streaming<V>(d_prenorm + idx, dp);
-                store_run_streaming<V>(d_norm_w + idx, gw);
-                store_run_streaming<V>(d_norm_b + idx, gb);
-            } else {
-                store_run<float, V>(grad + idx, true, gr);
-                store_run<float, V>(d_prenorm + idx, true, dp);
-                store_run<float, V>(d_norm_w + idx, true, gw);
-                store_run<float, V>(d_norm_b + idx, true, gb);
-            }
+            store_run<float, V>(grad + idx, true, gr);
+            store_run<float, V>(d_prenorm + idx, true, dp);
+            store_run<float, V>(d_norm_w + idx, true, gw);
+            store_run<float, V>(d_norm_b + idx, true, gb);
         }
-        if (d_prenorm_lp) store_run<T, V>(d_prenorm_lp + idx, true, dp);
+        if (d_prenorm_lp) {
+            float lp[V];
+#pragma unroll
+            for (int j = 0; j < V; ++j) lp[j] = dp[j] * kLpScale;
+            store_run<T, V>(d_prenorm_lp + idx, true, lp);
+        }
         if constexpr (V == 8) {
             if (sums && colsum_partial) {
 #pragma unroll
@@ -355,6 +347,7 @@ template <typename T, int KIND = -1, int REGU = -1> struct EpiWeightUpdate {
     T *w;
     float *master, *dv, *dm;   // master == (float*)w in f32 mode
     uint32_t N;
+    float gscale;              // accumulator -> batch sum of the unscaled gradient: 1/512, over kLpScale when dY is the 16-bit copy
     Optim opt;
     Hyper hyp;
     bool vec_ok;
@@ -377,7 +370,7 @@ template <typename T, int KIND = -1, int REGU = -1> struct EpiWeightUpdate {
             }
         }
 #pragma unroll
-        for (int j = 0; j < V; ++j) p[j] = optimiser_step(p[j], v[j], m[j], acc[j] * kLossScaleInv, opt, hyp, true);
+        for (int j = 0; j < V; ++j) p[j] = optimiser_step(p[j], v[j], m[j], acc[j] * gscale, opt, hyp, true);
         if (vec) {
             store_run<float, V>(dv + idx, true, v);
             store_run<float, V>(dm + idx, true, m);
@@ -410,7 +403,7 @@ template <typename T, int KIND = -1, int REGU = -1> struct EpiWeightUpdate {
         unpack<float, 8>(q.v, v);
         unpack<float, 8>(q.m, m);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) p[j] = optimiser_step_fast<KIND, REGU>(p[j], v[j], m[j], acc[j] * kLossScaleInv, opt, hyp, true);
+        for (int j = 0; j < 8; ++j) p[j] = optimiser_step_fast<KIND, REGU>(p[j], v[j], m[j], acc[j] * gscale, opt, hyp, true);
         store_run<float, 8>(dv + idx, true, v);
         store_run<float, 8>(dm + idx, true, m);
         store_run<float, 8>(master + idx, true, p);
@@ -422,12 +415,16 @@ template <typename T, int KIND = -1, int REGU = -1> struct EpiWeightUpdate {
 struct EpiStoreF32 {
     float *c;
     uint32_t N;
+    float scale;   // 1, or 1 / kLpScale when dY is the 16-bit copy
     bool vec_ok;
     template <int V>
     __device__ __forceinline__ void run(uint32_t row, uint32_t col0, const float (&acc)[V], uint32_t ncols) const {
         const size_t idx = (size_t)row * N + col0;
-        if (vec_ok && ncols == V) store_run<float, V>(c + idx, true, acc);
-        else for (uint32_t j = 0; j < ncols; ++j) c[idx + j] = acc[j];
+        float v[V];
+#pragma unroll
+        for (int j = 0; j < V; ++j) v[j] = acc[j] * scale;
+        if (vec_ok && ncols == V) store_run<float, V>(c + idx, true, v);
+        else for (uint32_t j = 0; j < ncols; ++j) c[idx + j] = v[j];
     }
 
     struct Cols {};
@@ -435,7 +432,7 @@ struct EpiStoreF32 {
     __device__ __forceinline__ void cols(uint32_t, Cols &) const {}
     __device__ __forceinline__ void prefetch(uint32_t, uint32_t, Pre &) const {}
     __device__ __forceinline__ void finish(uint32_t row, uint32_t col0, const float (&acc)[8], const Pre &, const Cols &) const {
-        store_run<float, 8>(c + (size_t)row * N + col0, true, acc);
+        run<8>(row, col0, acc, 8);
     }
 };
 

@@ -130,11 +130,110 @@ gemm_simt_kernel(const TA *__restrict__ A, const TB *__restrict__ B, uint32_t M,
     }
 }
 
-struct GemmOperand {
-    const void *ptr;
-    size_t ld;       // leading dimension in elements
-    bool contig_k;   // true: (mn, k) -> ptr[mn*ld + k]; false: ptr[k*ld + mn]
-};
+// The same product for large problems: 128 x 128 x 16 tiles, two shared-memory buffers (the next
+// panel is stored while the current one is still being read: one barrier per 16-deep step), 128-bit
+// shared-memory reads, and an 8 x 8 register block per thread laid out as 2 x 2 groups of 4 x 4, 64
+// apart, so that the 16 threads of a row read 256 contiguous bytes of the B panel (no bank conflicts)
+// and the two rows of a warp read two broadcast addresses of the A panel. Two blocks per SM. The
+// summation order per output is the same increasing-k chain, so results equal the kernel above bit for
+// bit. The epilogue functor gets runs of 4 consecutive columns.
+template <typename TA, typename TB, bool A_KCONTIG, bool B_NCONTIG, class Epi>
+__global__ void __launch_bounds__(kSimtThreads, 2)
+gemm_simt128_kernel(const TA *__restrict__ A, const TB *__restrict__ B, uint32_t M, uint32_t N, uint32_t K, size_t lda,
+                    size_t ldb, bool a_vec, bool b_vec, Epi epi) {
+    constexpr int BM = 128, BN = 128, BK = kSimtBK, E = BM * BK / kSimtThreads;   // 8 elements per thread per panel
+    constexpr int LD = BM + 4;
+    __shared__ __align__(16) float As[2][BK][LD];
+    __shared__ __align__(16) float Bs[2][BK][LD];
+
+    const int t = threadIdx.x;
+    const uint32_t m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int tx = t & 15, ty = t >> 4;
+
+    int a_mn, a_k, b_mn, b_k;
+    if (A_KCONTIG) { a_mn = t / (BK / E); a_k = (t % (BK / E)) * E; }
+    else           { a_k = t / (BM / E); a_mn = (t % (BM / E)) * E; }
+    if (B_NCONTIG) { b_k = t / (BN / E); b_mn = (t % (BN / E)) * E; }
+    else           { b_mn = t / (BK / E); b_k = (t % (BK / E)) * E; }
+
+    float ra[E], rb[E];
+    auto fetch = [&](uint32_t k0) {
+        if (A_KCONTIG) {
+            const uint32_t m = m0 + a_mn, k = k0 + a_k;
+            load_guarded<TA, E>(A + (size_t)m * lda + k, m < M ? (int)K - (int)k : 0, a_vec, ra);
+        } else {
+            const uint32_t m = m0 + a_mn, k = k0 + a_k;
+            load_guarded<TA, E>(A + (size_t)k * lda + m, k < K ? (int)M - (int)m : 0, a_vec, ra);
+        }
+        if (B_NCONTIG) {
+            const uint32_t n = n0 + b_mn, k = k0 + b_k;
+            load_guarded<TB, E>(B + (size_t)k * ldb + n, k < K ? (int)N - (int)n : 0, b_vec, rb);
+        } else {
+            const uint32_t n = n0 + b_mn, k = k0 + b_k;
+            load_guarded<TB, E>(B + (size_t)n * ldb + k, n < N ? (int)K - (int)k : 0, b_vec, rb);
+        }
+    };
+    auto stage = [&](int buf) {
+        if (A_KCONTIG) {
+#pragma unroll
+            for (int i = 0; i < E; ++i) As[buf][a_k + i][a_mn] = ra[i];
+        } else {
+            *reinterpret_cast<float4 *>(&As[buf][a_k][a_mn]) = make_float4(ra[0], ra[1], ra[2], ra[3]);
+            *reinterpret_cast<float4 *>(&As[buf][a_k][a_mn + 4]) = make_float4(ra[4], ra[5], ra[6], ra[7]);
+        }
+        if (B_NCONTIG) {
+            *reinterpret_cast<float4 *>(&Bs[buf][b_k][b_mn]) = make_float4(rb[0], rb[1], rb[2], rb[3]);
+            *reinterpret_cast<float4 *>(&Bs[buf][b_k][b_mn + 4]) = make_float4(rb[4], rb[5], rb[6], rb[7]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < E; ++i) Bs[buf][b_k + i][b_mn] = rb[i];
+        }
+    };
+
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+
+    fetch(0);
+    stage(0);
+    __syncthreads();
+    int buf = 0;
+    for (uint32_t k0 = 0; k0 < K; k0 += BK) {
+        const bool more = k0 + BK < K;
+        if (more) fetch(k0 + BK);
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            const float4 a0 = *reinterpret_cast<const float4 *>(&As[buf][kk][ty * 4]);
+            const float4 a1 = *reinterpret_cast<const float4 *>(&As[buf][kk][64 + ty * 4]);
+            const float4 b0 = *reinterpret_cast<const float4 *>(&Bs[buf][kk][tx * 4]);
+            const float4 b1 = *reinterpret_cast<const float4 *>(&Bs[buf][kk][64 + tx * 4]);
+            const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        if (more) stage(buf ^ 1);
+        __syncthreads();
+        buf ^= 1;
+    }
+
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t row = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
+        if (row >= M) continue;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t col0 = n0 + h * 64 + tx * 4;
+            if (col0 >= N) continue;
+            const float r[4] = {acc[i][h * 4], acc[i][h * 4 + 1], acc[i][h * 4 + 2], acc[i][h * 4 + 3]};
+            epi.template run<4>(row, col0, r, min(4u, N - col0));
+        }
+    }
+}
 
 // Host-side launcher: picks the tile so that small problems still spread over the SMs.
 template <typename TA, typename TB, bool A_KCONTIG, bool B_NCONTIG, class Epi>
@@ -147,7 +246,7 @@ cudaError_t launch_gemm_simt(cudaStream_t stream, int num_sms, const TA *A, size
     auto ctas = [&](uint32_t bm, uint32_t bn) { return (size_t)((M + bm - 1) / bm) * ((N + bn - 1) / bn); };
     if (ctas(128, 128) >= (size_t)num_sms) {
         dim3 grid((N + 127) / 128, (M + 127) / 128);
-        gemm_simt_kernel<TA, TB, A_KCONTIG, B_NCONTIG, 128, 128, 8, 8, Epi>
+        gemm_simt128_kernel<TA, TB, A_KCONTIG, B_NCONTIG, Epi>
             <<<grid, kSimtThreads, 0, stream>>>(A, B, M, N, K, lda, ldb, a_vec, b_vec, epi);
     } else if (ctas(64, 64) >= (size_t)num_sms) {
         dim3 grid((N + 63) / 64, (M + 63) / 64);

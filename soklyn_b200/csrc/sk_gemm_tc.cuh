@@ -57,11 +57,12 @@ enum : int { kTcErrProducer = 1, kTcErrMma = 2, kTcErrEpilogue = 3, kTcErrGate =
 
 // Optional gate on the B operand (data-parallel backward): the rows of B arrive from other GPUs in
 // `chunks` blocks of `rows_per_chunk` rows, and flags[chunk * stride + rank] reaches `epoch` once that
-// rank's part of the block has landed in this GPU's memory. The producer waits (bounded) for every rank's
+// rank's part of the block has landed in this GPU's memory (this GPU's own part is complete before the
+// launch, by stream order). The producer waits (bounded) for every rank's
 // flag of the blocks a tile needs before it issues the loads. flags == nullptr: no gate.
 struct TcGate {
     const uint32_t *flags;
-    uint32_t world, stride, chunks, rows_per_chunk, epoch;
+    uint32_t world, self, stride, chunks, rows_per_chunk, epoch;   // `self`: the rank whose rows are ordered by the stream
 };
 
 // Bounded wait until *flag (system-scope acquire) has reached `value` in wrap-around order.
@@ -141,7 +142,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     if (ready_chunks < need) {
                         while (ready_chunks < need && gate_ok) {
                             for (uint32_t r = 0; r < gate.world && gate_ok; ++r)
-                                gate_ok = wait_flag_reached(gate.flags + ready_chunks * gate.stride + r, gate.epoch);
+                                if (r != gate.self) gate_ok = wait_flag_reached(gate.flags + ready_chunks * gate.stride + r, gate.epoch);
                             ++ready_chunks;
                         }
                         if (!gate_ok) { ok = false; break; }

@@ -292,7 +292,7 @@ output_error_kernel(T *__restrict__ out, const T *__restrict__ preact, const T *
         d_prenorm[idx] = dp;
         d_norm_w[idx] = g.d_norm_w;
         d_norm_b[idx] = g.d_norm_b;
-        if (d_prenorm_lp) d_prenorm_lp[idx] = from_f32<T>(dp);
+        if (d_prenorm_lp) d_prenorm_lp[idx] = from_f32<T>(dp * kLpScale);
     }
 }
 
@@ -338,7 +338,12 @@ output_error_elem_kernel(const T *__restrict__ out, const T *__restrict__ preact
         store_run<float, V>(d_prenorm + idx, true, dp);
         store_run<float, V>(d_norm_w + idx, true, gw);
         store_run<float, V>(d_norm_b + idx, true, gb);
-        if (d_prenorm_lp) store_run<T, V>(d_prenorm_lp + idx, true, dp);
+        if (d_prenorm_lp) {
+            float lp[V];
+#pragma unroll
+            for (int j = 0; j < V; ++j) lp[j] = dp[j] * kLpScale;
+            store_run<T, V>(d_prenorm_lp + idx, true, lp);
+        }
     }
 }
 
@@ -427,9 +432,11 @@ __device__ __forceinline__ void vector_step(const VectorParams<T> &P, uint32_t c
 
 // `nblocks` partial slabs [3 x N] are summed first (1 slab for finished sums), then the step.
 template <typename T>
-__global__ void vector_update_kernel(const float *__restrict__ partial, uint32_t nblocks, uint32_t N, VectorParams<T> P) {
+__global__ void vector_update_kernel(const float *__restrict__ partial, uint32_t nblocks, uint32_t N, VectorParams<T> P,
+                                     const int *abort_flag = nullptr) {
     const uint32_t col = blockIdx.x * blockDim.x + threadIdx.x;
     if (col >= N) return;
+    if (abort_flag && *reinterpret_cast<const volatile int *>(abort_flag) != 0) return;   // the sums are not complete
     float s[3] = {0.0f, 0.0f, 0.0f};
     for (uint32_t k = 0; k < nblocks; ++k)
 #pragma unroll
@@ -500,12 +507,14 @@ weight_update_kernel(const float *__restrict__ dw, T *w, float *master, float *d
 // Weight step on a contiguous range of elements from a gradient stored as G (f32 or the
 // 16-bit storage type), already averaged over the batch: g = grad * grad_scale (the remaining
 // loss-scale factor). Used by the sharded data-parallel update, where each rank steps 1/W of
-// every weight matrix.
+// every weight matrix. With `abort_flag` given, a non-zero word there (a bounded wait of an earlier
+// kernel gave up, so `grad` is not complete) makes the kernel leave everything untouched.
 template <typename T, typename G>
 __global__ void __launch_bounds__(kRowThreads)
 weight_update_range_kernel(const G *__restrict__ grad, float grad_scale, T *w, float *master, float *dv, float *dm,
-                           size_t len, Optim opt, Hyper hyp, bool vec_ok) {
+                           size_t len, Optim opt, Hyper hyp, bool vec_ok, const int *abort_flag = nullptr) {
     constexpr int V = 8;
+    if (abort_flag && *reinterpret_cast<const volatile int *>(abort_flag) != 0) return;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     if (vec_ok) {
         for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < len / V; i += stride) {

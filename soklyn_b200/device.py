@@ -94,7 +94,7 @@ class GpuContext:
     def launch_count(self) -> int:
         return int(self.lib.sk_launch_count(self.handle))
 
-    PROFILE_CLASSES = ("gemm_forward", "gemm_dx", "gemm_dw", "norm", "output_error", "colsum", "update")
+    PROFILE_CLASSES = ("gemm_forward", "gemm_dx", "gemm_dw", "norm", "output_error", "colsum", "update", "exchange")
 
     def profile_enable(self, on: bool = True):
         self._check(self.lib.sk_profile_enable(self.handle, int(on)))
@@ -221,8 +221,11 @@ class GpuContext:
     def dp_flag_bytes(self) -> int:
         return int(self.lib.sk_dp_flag_bytes())
 
+    def dp_scratch_bytes(self, k: int, n: int, world: int) -> int:
+        return int(self.lib.sk_dp_scratch_bytes(k, n, world))
+
     def gpu_dp_backward(self, layers, tables, target: Tensor, input: Tensor, loss_config, train_ctx, batch: int,
-                        batch_stat: int, world: int, rank: int, blocks: int, epoch: int, step: int):
+                        batch_stat: int, world: int, rank: int, blocks: int, epoch: int, step: int, scratch: torch.Tensor):
         n = len(layers)
         ptrs = (C.c_void_p * n)(*[C.addressof(l.desc()) for l in layers])
         lin = (SkOptim * n)(*[_optim(o) for o in train_ctx.optimisers])
@@ -231,7 +234,8 @@ class GpuContext:
         self._check(self.lib.sk_dp_backward(self.handle, ptrs, tables, n, target.ptr(), target.rows(), input.ptr(),
                                             input.rows(), loss_config.loss_func.value, act.ordinal(), act.coeff, lin, nrm,
                                             batch, batch_stat, world, rank, blocks, epoch & 0xFFFFFFFF,
-                                            train_ctx.learn_rate, train_ctx.grad_clamp, step & 0xFFFFFFFF))
+                                            train_ctx.learn_rate, train_ctx.grad_clamp, step & 0xFFFFFFFF,
+                                            scratch.data_ptr(), scratch.numel() * scratch.element_size()))
 
     # -- fused exchange over peer-mapped buffers (no counterpart in the reference) --
     def gpu_reduce_update_broadcast(self, layer, peer_grad, world: int, rank: int, peer_w, train_ctx, step: int):

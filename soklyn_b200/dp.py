@@ -145,6 +145,8 @@ class DataParallelFFN:
             self.sharded = [True] * len(layers)
             self.blocks = [context.dp_blocks(l.get_weights().rows(), l.get_weights().cols(), world, want) for l in layers]
             self.want_blocks = want
+            need = max(context.dp_scratch_bytes(l.get_weights().rows(), l.get_weights().cols(), world) for l in layers)
+            self.scratch = torch.empty((need + 3) // 4, device=dev, dtype=torch.float32)   # summed gradient rows, column sums
         if self.fused or self.pipelined:
             self.dw, self.dw_shard = [], []      # these exchanges stage gradients in their own arena
             self._map_peers(layers)
@@ -319,7 +321,7 @@ class DataParallelFFN:
         if self.pipelined:
             self.net._check_backward(target, input, loss_config, _LocalBatch(train_ctx, self.local_batch))
             self.ctx.gpu_dp_backward(layers, self._exchange_tables(), target, input, loss_config, train_ctx, self.local_batch,
-                                     self.global_batch, self.world, self.rank, self.want_blocks, self.epoch, step)
+                                     self.global_batch, self.world, self.rank, self.want_blocks, self.epoch, step, self.scratch)
             return
         layers[last].compute_loss(self.ctx, target, loss_config)
         for i in range(last, -1, -1):

@@ -72,12 +72,12 @@ def main():
         dp.close()   # also completes the sharded masters and moments on every rank (gather_state)
         for i, layer in enumerate(net.get_layers()):
             for getter in ("get_master_weights", "get_dv_weights", "get_dm_weights"):
-                t = getattr(layer, getter)()
-                if t is None:
+                state = getattr(layer, getter)()
+                if state is None:
                     continue
-                ref = t.data.clone()
+                ref = state.data.clone()
                 dist.broadcast(ref, 0)
-                assert torch.equal(t.data, ref), f"{spec.name}: layer {i} {getter} differs between ranks after gather_state"
+                assert torch.equal(state.data, ref), f"{spec.name}: layer {i} {getter} differs between ranks after gather_state"
             if layer.get_master_weights() is not None:   # the 16-bit weights are the rounded masters, row for row
                 assert torch.equal(layer.get_master_weights().data.to(layer.get_weights().data.dtype), layer.get_weights().data), \
                     f"{spec.name}: layer {i} weights are not the rounded master weights"
