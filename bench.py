@@ -171,7 +171,8 @@ def run_ours(args):
         ctx.set_lean_backward(True)
     local = spec.batch // world
     net = configs.build_network(ctx, spec, max_batch=local)
-    dp = DataParallelFFN(ctx, net, spec.batch, rank, world, scheme=args.dp_scheme, chunks=args.dp_chunks)
+    dp = DataParallelFFN(ctx, net, spec.batch, rank, world, scheme=args.dp_scheme, chunks=args.dp_chunks,
+                         multicast={"on": True, "off": False, "auto": "auto"}[args.dp_multicast] if world > 1 else False)
     x, t, _ = configs.make_data(spec)
     r0 = rank * local
     prec = spec.prec()
@@ -470,8 +471,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gemm-sweep", action="store_true", help="leave the M = 16384 DenseBlock GEMM shapes out of the line")
     ap.add_argument("--lean", action="store_true", help="SK_OPTION_LEAN_BACKWARD (not the headline configuration)")
-    ap.add_argument("--dp-chunks", type=int, default=0, help="row blocks per layer of the pipelined exchange (0: automatic)")
-    ap.add_argument("--dp-scheme", default="auto", choices=["auto", "pipelined", "fused", "sharded", "allreduce"],
+    ap.add_argument("--dp-multicast", default="auto", choices=["auto", "on", "off"],
+                    help="exchange arena in symmetric memory: in-switch reduction and multicast stores where the node has them")
+    ap.add_argument("--dp-chunks", type=int, default=0, help="row blocks per layer of the native exchange (0: one)")
+    ap.add_argument("--dp-scheme", default="auto", choices=["auto", "native", "fused", "sharded", "allreduce"],
                     help="gradient exchange of the data-parallel runs (see soklyn_b200/dp.py)")
     ap.add_argument("--sweep-m", default="256,1024,4096,16384,65536")
     ap.add_argument("--sweep-kn", default="1024,4096,8192")

@@ -110,7 +110,7 @@ int sk_ctx_set_stream(sk_ctx *ctx, void *stream);
  * 16-bit d_prenorm_lp. A deviation from the reference, whose getters expose those tensors
  * (src/mlp.rs:446-454): they keep stale contents. Parameters come out bit-identical. Off by default.
  * SK_OPTION_RESERVE_SMS: number of SMs the tensor-core GEMMs leave free, so that a kernel on another
- * stream (the data-parallel exchange) can run beside them. 0 by default. */
+ * stream can run beside them. 0 by default. */
 enum { SK_OPTION_GEMM_ENGINE = 0, SK_OPTION_COLSUM_HANDOVER = 1, SK_OPTION_LEAN_BACKWARD = 2, SK_OPTION_RESERVE_SMS = 3 };
 int sk_ctx_set_option(sk_ctx *ctx, uint32_t option, uint32_t value);
 /* Grow the scratch workspace; never called implicitly. */
@@ -224,40 +224,42 @@ int sk_apply_vector_update(sk_ctx *ctx, const sk_dense *layer, const float *cols
 int sk_reduce_update_broadcast(sk_ctx *ctx, const sk_dense *layer, void *const *peer_grad, uint32_t world,
                                uint32_t rank, void *const *peer_w, const sk_optim *linear, float learn_rate,
                                float grad_clamp, uint32_t step);
-/* Pipelined form of the same exchange, the whole backward pass of a network in one call (no counterpart;
- * the order kept is the reference's, src/ffn.rs:113-166: every hidden delta reads the next layer's weights
- * after their update). Each weight matrix is exchanged in `blocks` blocks of rows (sk_dp_blocks gives the
- * count actually used for a shape: the largest <= blocks that splits evenly; 0 = the shape cannot be
- * split); inside a block rank r owns rows [r*K/(blocks*world), (r+1)*K/(blocks*world)) and keeps f32
- * masters and moments current for those rows only. Per block: the dW GEMM writes the block of the local
- * 16-bit gradient; a kernel on a second stream (on SMs the GEMMs leave free) pulls the owned rows from
- * every rank and adds them; the optimiser step of those rows runs on the context's stream; a second kernel
- * on the second stream stores the new 16-bit rows into every other rank's weight tensor; and the dX GEMM of
- * the layer below waits, inside its TMA producer, only for the blocks of rows its tile needs. The last
- * block's reduction also adds the [3 x N] column sums of all ranks for the bias / normalisation-parameter
- * step. Work of one GPU is ordered by streams and events; kernels wait only for flags raised by OTHER GPUs,
- * and every such wait is bounded (SK_ERR_DEVICE_TIMEOUT at the next sk_sync; after a wait gave up no weight
- * is changed and no flag raised). Per layer the caller provides, for every rank as mapped into this
- * process: the gradient buffer T [K x N], the weight tensor T [K x N] (this rank's entry must be the
- * block's `w`), sk_dp_flag_bytes() bytes of flag words (zero at set-up), and a column-sum buffer f32
- * [3 x N]; plus local scratch of at least sk_dp_scratch_bytes(K, N, world) bytes for the largest layer
- * (256-byte aligned). `epoch` must grow by one per call. 16-bit blocks without BatchNorm; world = 2, 4 or
- * 8. When the call returns, later work on the context's stream is ordered after the whole exchange. */
+/* The same exchange for a whole network in one call: the data-parallel backward pass sequenced in native
+ * code (no counterpart; the order kept is the reference's, src/ffn.rs:113-166: every hidden delta reads the
+ * next layer's weights after their update). Each weight matrix is exchanged in `blocks` blocks of rows
+ * (sk_dp_blocks gives the count actually used for a shape: the largest <= blocks that splits evenly; 0 = the
+ * shape cannot be split; blocks = 0 means 1); inside a block rank r owns rows [r*K/(blocks*world),
+ * (r+1)*K/(blocks*world)) and keeps f32 masters and moments current for those rows only. Per block: the dW
+ * GEMM writes the block of the local 16-bit gradient and raises a flag on the other ranks; one kernel waits
+ * for their flags, obtains the sum of the owned rows (peer loads and adds, or one in-switch reduction per 16
+ * bytes when mc_grad / mc_w are given), steps them and stores the new 16-bit rows into every rank's weight
+ * tensor; and the dX GEMM of the layer below waits, inside its TMA producer, only for the blocks of rows its
+ * tile needs. The last block's kernel also adds the [3 x N] column sums of all ranks and steps bias and
+ * normalisation parameters. Everything runs on the context's stream; kernels wait only for flags raised by
+ * OTHER GPUs, and every such wait is bounded (SK_ERR_DEVICE_TIMEOUT at the next sk_sync; after a wait gave
+ * up no weight is changed and no flag raised). Per layer the caller provides, for every rank as mapped into
+ * this process: the gradient buffer T [K x N], the weight tensor T [K x N] (this rank's entry must be the
+ * block's `w`), sk_dp_flag_bytes() bytes of flag words (zero at set-up), and a column-sum buffer f32 [3 x N].
+ * `epoch` must grow by one per call. 16-bit blocks without BatchNorm; world = 2, 4 or 8. */
 typedef struct {
     void *const *peer_grad;
     void *const *peer_w;
     void *const *peer_flags;
     void *const *peer_colsums;
+    /* Optional: addresses of the gradient buffers / weight tensors inside an NVSwitch multicast mapping that
+     * covers the same arenas on all ranks (NULL = plain peer loads and stores). With them the reduction runs
+     * inside the switch (multimem.ld_reduce, f32 accumulation, sum returned in the 16-bit type) and a rank's
+     * rows are sent once (multimem.st). Do not use in a job in which a rank may leave. */
+    void *mc_grad;
+    void *mc_w;
 } sk_exchange;
 uint32_t sk_dp_blocks(uint32_t K, uint32_t N, uint32_t world, uint32_t blocks);
 uint32_t sk_dp_flag_bytes(void);
-size_t sk_dp_scratch_bytes(uint32_t K, uint32_t N, uint32_t world);
 int sk_dp_backward(sk_ctx *ctx, const sk_dense *const *layers, const sk_exchange *exchange, uint32_t n_layers,
                    const void *target, uint32_t target_rows, const void *x, uint32_t x_rows, uint32_t loss,
                    uint32_t loss_act, float loss_leaky, const sk_optim *linear, const sk_optim *norm_opt,
                    uint32_t batch, uint32_t batch_stat, uint32_t world, uint32_t rank, uint32_t blocks,
-                   uint32_t epoch, float learn_rate, float grad_clamp, uint32_t step, float *scratch,
-                   size_t scratch_bytes);
+                   uint32_t epoch, float learn_rate, float grad_clamp, uint32_t step);
 
 /* Exchange arena of one rank: sk_peer_alloc allocates `bytes` of zeroed device memory (set-up time,
  * not the hot path) and returns a 64-byte CUDA IPC handle for it; the other ranks (other processes
@@ -281,7 +283,9 @@ int sk_wait_flags(sk_ctx *ctx, const uint32_t *flags, uint32_t world, uint32_t v
  * live in a 3 MiB array built into the library (present on every GPU that loads it), which
  * limits N to 262144 columns: beyond that the call returns SK_ERR_STATIC_LIMIT. Calls share
  * that array, so calls that overlap on the GPU race and must be serialised by the caller.
- * The first call on a device resolves the array's address; make it before any stream capture.
+ * The first call on a device resolves the array's address; make it before any stream capture, and from
+ * one host thread (concurrent first calls on a device all store the same pointer, which is harmless, but
+ * it is a data race by the letter).
  * `stream` is a cudaStream_t (NULL = legacy default stream); norm selects which sums are
  * taken (0: dB only, 1: + d_norm_w, 2/3: + d_norm_b), unused inputs may be NULL. */
 int sk_column_sums_static(void *stream, const float *d_prenorm, const float *d_norm_w,

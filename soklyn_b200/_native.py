@@ -51,7 +51,8 @@ class SkDense(C.Structure):
 
 class SkExchange(C.Structure):
     """Per-layer pointer tables of sk_dp_backward: arrays of `world` device pointers, one per rank."""
-    _fields_ = [("peer_grad", C.c_void_p), ("peer_w", C.c_void_p), ("peer_flags", C.c_void_p), ("peer_colsums", C.c_void_p)]
+    _fields_ = [("peer_grad", C.c_void_p), ("peer_w", C.c_void_p), ("peer_flags", C.c_void_p), ("peer_colsums", C.c_void_p),
+                ("mc_grad", C.c_void_p), ("mc_w", C.c_void_p)]
 
 
 def sources() -> list[str]:
@@ -137,8 +138,7 @@ _SIGS = {
     "sk_dp_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p,
                                  C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, C.c_void_p, C.c_void_p, C.c_uint32,
                                  C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, C.c_float,
-                                 C.c_uint32, C.c_void_p, C.c_size_t]),
-    "sk_dp_scratch_bytes": (C.c_size_t, [C.c_uint32, C.c_uint32, C.c_uint32]),
+                                 C.c_uint32]),
     "sk_copy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
     "sk_peer_alloc": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p]),
     "sk_peer_open": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p)]),

@@ -40,12 +40,8 @@ struct sk_ctx {
     uint32_t tc_group_n = 8;               // tile columns walked together (SK_TC_GROUP_N at context creation)
     uint32_t reserve_sms = 0;              // SMs the tensor-core GEMMs leave free (for a concurrent exchange kernel)
     bool lean = false;                     // SK_OPTION_LEAN_BACKWARD
-    // pipelined data-parallel backward
-    cudaStream_t comm_stream = nullptr;    // exchange kernels run here, beside the GEMMs
-    cudaEvent_t comm_done = nullptr;
+    // data-parallel backward
     uint32_t *dp_counters = nullptr;       // one completion counter per (layer, block), zero between launches
-    std::vector<cudaEvent_t> dp_events;    // per block: dW written / reduced / stepped
-    uint32_t dp_reserve_override = 0;      // SK_DP_RESERVE_SMS at context creation (0: by rank count)
     // Column sums handed from the dX epilogue to the weight update of the same layer. Only inside
     // sk_ffn_backward (nothing can touch the tensors or the workspace in between there).
     bool in_ffn_backward = false;
@@ -637,7 +633,7 @@ int apply_update_impl(sk_ctx *c, const sk_dense *L, const float *dw, const float
     return check_cuda(c, cudaGetLastError(), "weight step");
 }
 
-// ---- pipelined data-parallel backward ----------------------------------------------------------
+// ---- data-parallel backward in one call ----------------------------------------------------------
 
 // Blocks of rows a [K x N] weight matrix is exchanged in: the largest count <= wanted for which every
 // rank owns whole rows of every block and its part is a whole number of 16-byte runs.
@@ -661,66 +657,23 @@ int dw_rows_lp(sk_ctx *c, const sk_dense *L, const void *x, uint32_t batch, uint
     return rc;
 }
 
-constexpr int kExchangeSmem = 120 * 1024;   // more than half an SM's shared memory: one block per SM, none beside a GEMM block
-
-template <class Kernel> cudaError_t exclusive_smem_attr(sk_ctx *c, Kernel kernel, uint64_t (&attr_set)[4]) {
-    const unsigned dev = (unsigned)c->device & 255u;
-    if (attr_set[dev >> 6] >> (dev & 63) & 1ull) return cudaSuccess;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kExchangeSmem);
-    if (e == cudaSuccess) attr_set[dev >> 6] |= 1ull << (dev & 63);
-    return e;
-}
-
-template <typename T, int W> cudaError_t launch_reduce(sk_ctx *c, const ReduceArgs &a, uint32_t ctas) {
-    static uint64_t attr_set[4] = {0, 0, 0, 0};
-    cudaError_t e = exclusive_smem_attr(c, reduce_rows_kernel<T, W>, attr_set);
-    if (e != cudaSuccess) return e;
-    reduce_rows_kernel<T, W><<<ctas, kExchangeThreads, kExchangeSmem, c->comm_stream>>>(a);
+template <typename T, int W>
+cudaError_t launch_exchange(sk_ctx *c, const ExchangeArgs<T> &a) {
+    size_t blocks = (a.len / 8 + kRowThreads - 1) / kRowThreads;
+    const size_t cap = (size_t)c->num_sms * 8;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    if (a.mc_grad && a.mc_w) exchange_update_kernel<T, W, true><<<(uint32_t)blocks, kRowThreads, 0, c->stream>>>(a);
+    else exchange_update_kernel<T, W, false><<<(uint32_t)blocks, kRowThreads, 0, c->stream>>>(a);
     return cudaGetLastError();
-}
-template <typename T, int W> cudaError_t launch_spread(sk_ctx *c, const SpreadArgs &a, uint32_t ctas) {
-    static uint64_t attr_set[4] = {0, 0, 0, 0};
-    cudaError_t e = exclusive_smem_attr(c, spread_rows_kernel<T, W>, attr_set);
-    if (e != cudaSuccess) return e;
-    spread_rows_kernel<T, W><<<ctas, kExchangeThreads, kExchangeSmem, c->comm_stream>>>(a);
-    return cudaGetLastError();
-}
-template <typename T> cudaError_t launch_reduce_w(sk_ctx *c, uint32_t world, const ReduceArgs &a, uint32_t ctas) {
-    switch (world) {
-    case 2: return launch_reduce<T, 2>(c, a, ctas);
-    case 4: return launch_reduce<T, 4>(c, a, ctas);
-    case 8: return launch_reduce<T, 8>(c, a, ctas);
-    default: return cudaErrorInvalidValue;
-    }
-}
-template <typename T> cudaError_t launch_spread_w(sk_ctx *c, uint32_t world, const SpreadArgs &a, uint32_t ctas) {
-    switch (world) {
-    case 2: return launch_spread<T, 2>(c, a, ctas);
-    case 4: return launch_spread<T, 4>(c, a, ctas);
-    case 8: return launch_spread<T, 8>(c, a, ctas);
-    default: return cudaErrorInvalidValue;
-    }
-}
-
-// Event `kind` (0: block of dW written, 1: block reduced, 2: block stepped) of block `ch`; created on first use.
-cudaEvent_t dp_event(sk_ctx *c, uint32_t ch, uint32_t kind) {
-    const size_t idx = (size_t)ch * 3 + kind;
-    if (c->dp_events.size() <= idx) c->dp_events.resize(idx + 1, nullptr);
-    if (!c->dp_events[idx]) cudaEventCreateWithFlags(&c->dp_events[idx], cudaEventDisableTiming);
-    return c->dp_events[idx];
 }
 
 template <typename T>
 int dp_backward_impl(sk_ctx *c, const sk_dense *const *layers, const sk_exchange *ex, uint32_t n, const void *target,
                      uint32_t target_rows, const void *x, uint32_t x_rows, uint32_t loss, uint32_t loss_act,
                      float loss_leaky, const sk_optim *lin_, const sk_optim *nrm_, uint32_t batch, uint32_t batch_stat,
-                     uint32_t world, uint32_t rank, uint32_t chunks, uint32_t epoch, float lr, float clamp, uint32_t step,
-                     float *scratch) {
+                     uint32_t world, uint32_t rank, uint32_t chunks, uint32_t epoch, float lr, float clamp, uint32_t step) {
     const uint32_t last = n - 1;
-    uint32_t reserve = c->dp_reserve_override ? c->dp_reserve_override : (world <= 2 ? 8u : world <= 4 ? 16u : 20u);
-    if (reserve >= (uint32_t)c->num_sms) reserve = (uint32_t)c->num_sms / 4;
-    const uint32_t saved_reserve = c->reserve_sms;
-    c->reserve_sms = reserve;
     int rc = sk_output_error(c, layers[last], target, target_rows, layers[last]->max_batch, loss, loss_act, loss_leaky);
     uint32_t p_next = 0;   // blocks of layer i + 1
     for (uint32_t ii = n; ii-- > 0 && rc == SK_OK;) {
@@ -745,7 +698,7 @@ int dp_backward_impl(sk_ctx *c, const sk_dense *const *layers, const sk_exchange
             c->in_ffn_backward = false;
             if (rc) break;
         }
-        // column sums of this rank's rows into its arena (the other ranks read them in the last block's reduction)
+        // column sums of this rank's rows into its arena (the other ranks read them in the last block's kernel)
         uint32_t nslabs = 0;
         const float *slabs = column_sum_slabs(c, L, batch, &nslabs, &rc);
         if (rc) break;
@@ -755,80 +708,51 @@ int dp_backward_impl(sk_ctx *c, const sk_dense *const *layers, const sk_exchange
 
         const uint32_t P = dp_chunks_for(L->K, L->N, world, chunks);
         const uint32_t rows_block = L->K / P, rows_own = rows_block / world;
-        const size_t own_len = (size_t)rows_own * L->N;
         const Optim lin = make_optim(&lin_[ii], step), nrm = make_optim(&nrm_[ii], step);
-        const Hyper hyp_w{lr, clamp, 1.0f, L->regu, L->regu_coeff};   // the staged gradients are already averaged
-        float *colsum_total = scratch;                                 // [3 x N], then the summed rows of every block
-        float *gsum = scratch + (((size_t)3 * L->N + 63) / 64) * 64;
-        ReduceArgs ra{};
-        SpreadArgs sa{};
+        ExchangeArgs<T> a{};
         PeerPtrs pf{};
         for (uint32_t r = 0; r < world; ++r) {
-            ra.grad.p[r] = E.peer_grad[r]; ra.flags.p[r] = E.peer_flags[r]; ra.colsums.p[r] = E.peer_colsums[r];
-            sa.w.p[r] = E.peer_w[r]; sa.flags.p[r] = E.peer_flags[r];
+            a.grad.p[r] = E.peer_grad[r]; a.w.p[r] = E.peer_w[r]; a.flags.p[r] = E.peer_flags[r]; a.colsums.p[r] = E.peer_colsums[r];
             pf.p[r] = E.peer_flags[r];
         }
-        ra.world = sa.world = world; ra.rank = sa.rank = rank; ra.epoch = sa.epoch = epoch;
-        ra.err = c->tc_err; sa.err = c->tc_err; ra.N = L->N; ra.colsum_total = colsum_total;
-        T *w = (T *)L->w;
-        float *master = master_of<T>(L->master_w, L->w);
-        auto own_off = [&](uint32_t ch) { return ((size_t)ch * rows_block + (size_t)rank * rows_own) * L->N; };
-        // the optimiser step of block `ch` (main stream, every SM) and its all-gather (second stream)
-        auto step_and_spread = [&](uint32_t ch) -> int {
-            const size_t off = own_off(ch);
-            cudaStreamWaitEvent(c->stream, dp_event(c, ch, 1), 0);
-            const bool vec = own_len % 8 == 0 && aligned16(gsum) && aligned16(w + off) && aligned16(master + off);
-            size_t blocks = (own_len / 8 + kRowThreads - 1) / kRowThreads;
-            const size_t cap = (size_t)c->num_sms * 8;
-            if (blocks > cap) blocks = cap;
-            if (blocks < 1) blocks = 1;
-            {
-                ProfScope ps(c, SK_PROF_UPDATE);
-                weight_update_range_kernel<T, float><<<(uint32_t)blocks, kRowThreads, 0, c->stream>>>(
-                    gsum + (size_t)ch * own_len, kLossScaleInv, w + off, master + off, L->dv_w + off, L->dm_w + off, own_len, lin,
-                    hyp_w, vec, c->tc_err);
+        a.mc_grad = E.mc_grad; a.mc_w = E.mc_w;
+        a.world = world; a.rank = rank; a.epoch = epoch;
+        a.master = master_of<T>(L->master_w, L->w); a.dv = L->dv_w; a.dm = L->dm_w;
+        a.opt = lin; a.hyp = Hyper{lr, clamp, 1.0f, L->regu, L->regu_coeff};   // the staged gradients are already averaged
+        a.err = c->tc_err; a.N = L->N;
+        a.vp = vector_params<T>(L, lin, nrm, Hyper{lr, clamp, 1.0f / (float)batch_stat, L->regu, L->regu_coeff});
+        auto exchange = [&](uint32_t ch) -> int {
+            a.chunk = ch;
+            a.off = ((size_t)ch * rows_block + (size_t)rank * rows_own) * L->N;
+            a.len = (size_t)rows_own * L->N;
+            a.done = c->dp_counters + ii * kMaxChunks + ch;
+            a.do_vector = ch == P - 1;
+            ProfScope ps(c, SK_PROF_EXCHANGE);
+            cudaError_t e;
+            switch (world) {
+            case 2: e = launch_exchange<T, 2>(c, a); break;
+            case 4: e = launch_exchange<T, 4>(c, a); break;
+            case 8: e = launch_exchange<T, 8>(c, a); break;
+            default: e = cudaErrorInvalidValue;
             }
-            c->launches++;
-            cudaEventRecord(dp_event(c, ch, 2), c->stream);
-            cudaStreamWaitEvent(c->comm_stream, dp_event(c, ch, 2), 0);
-            sa.chunk = ch; sa.off = off; sa.len = own_len; sa.done = c->dp_counters + ii * kMaxChunks + ch;
-            ProfScope ps(c, SK_PROF_EXCHANGE, c->comm_stream);
-            const cudaError_t e = launch_spread_w<T>(c, world, sa, reserve);
-            c->launches++;
-            return check_cuda(c, e, "all-gather kernel");
+            c->launches++; c->tc_launches++;
+            return check_cuda(c, e, "exchange kernel");
         };
+        // the exchange of a block is issued after the GEMM of the next one, so that the other ranks' flags of the
+        // block have had a GEMM's time to arrive before a kernel waits for them
         for (uint32_t ch = 0; ch < P && rc == SK_OK; ++ch) {
             if ((rc = dw_rows_lp<T>(c, L, in, batch, batch_stat, E.peer_grad[rank], ch * rows_block, rows_block))) break;
             signal_chunk_kernel<<<1, 32, 0, c->stream>>>(pf, world, rank, (0 * kMaxChunks + ch) * kMaxRanks + rank, epoch);
             c->launches++;
-            cudaEventRecord(dp_event(c, ch, 0), c->stream);
-            cudaStreamWaitEvent(c->comm_stream, dp_event(c, ch, 0), 0);
-            ra.chunk = ch; ra.off = own_off(ch); ra.len = own_len; ra.sum = gsum + (size_t)ch * own_len;
-            ra.do_colsums = ch == P - 1;
-            {
-                ProfScope ps(c, SK_PROF_EXCHANGE, c->comm_stream);
-                const cudaError_t e = launch_reduce_w<T>(c, world, ra, reserve);
-                c->launches++; c->tc_launches++;
-                if ((rc = check_cuda(c, e, "reduce-scatter kernel"))) break;
-            }
-            cudaEventRecord(dp_event(c, ch, 1), c->comm_stream);
-            if (ch >= 1 && (rc = step_and_spread(ch - 1))) break;
+            if (ch >= 1) rc = exchange(ch - 1);
         }
-        if (rc == SK_OK) rc = step_and_spread(P - 1);
-        if (rc) break;
-        // bias and normalisation parameters from the column sums of all ranks (summed by the last block's reduction,
-        // which the wait for that block's event above has ordered before this)
-        const Hyper hyp_v{lr, clamp, 1.0f / (float)batch_stat, L->regu, L->regu_coeff};
-        rc = vector_update_launch<T>(c, L, colsum_total, 1, lin, nrm, hyp_v, c->tc_err);
+        if (rc == SK_OK) rc = exchange(P - 1);
         p_next = P;
     }
     c->fused_colsum_key = nullptr;
-    c->reserve_sms = saved_reserve;
     if (rc) return rc;
-    // the step is complete when this rank's exchange kernels have finished and every other rank's rows of the
-    // first layer have landed here (the deltas above already waited for the other layers' rows)
-    cudaEventRecord(c->comm_done, c->comm_stream);
-    cudaStreamWaitEvent(c->stream, c->comm_done, 0);
+    // the step is complete when every other rank's rows of the first layer have landed here (the deltas above
+    // already waited for the other layers' rows)
     const uint32_t *flags_b0 = reinterpret_cast<const uint32_t *>(ex[0].peer_flags[rank]) + kMaxChunks * kMaxRanks;
     wait_words_kernel<<<1, 64, 0, c->stream>>>(flags_b0, p_next, kMaxRanks, world, rank, epoch, c->tc_err);
     c->launches++; c->tc_launches++;
@@ -869,7 +793,6 @@ int sk_ctx_create(int device, uint32_t tile_dim, void *stream, int create_stream
     cudaFuncSetAttribute(sk::norm_rows_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
     c->cc_major = prop.major;
     if (const char *env = getenv("SK_TC_GROUP_N")) { const int v = atoi(env); if (v >= 1 && v <= 64) c->tc_group_n = (uint32_t)v; }
-    if (const char *env = getenv("SK_DP_RESERVE_SMS")) { const int v = atoi(env); if (v >= 1 && v < c->num_sms) c->dp_reserve_override = (uint32_t)v; }
     {
         cudaDriverEntryPointQueryResult q;
         void *fn = nullptr;
@@ -902,9 +825,6 @@ void sk_ctx_destroy(sk_ctx *c) {
     if (c->workspace) cudaFree(c->workspace);
     if (c->tc_err) cudaFree(c->tc_err);
     if (c->dp_counters) cudaFree(c->dp_counters);
-    if (c->comm_stream) { cudaStreamSynchronize(c->comm_stream); cudaStreamDestroy(c->comm_stream); }
-    if (c->comm_done) cudaEventDestroy(c->comm_done);
-    for (cudaEvent_t e : c->dp_events) if (e) cudaEventDestroy(e);
     for (cudaEvent_t e : c->ev_pool) cudaEventDestroy(e);
     if (c->own_stream) cudaStreamDestroy(c->stream);
     delete c;
@@ -1223,22 +1143,15 @@ uint32_t sk_dp_blocks(uint32_t K, uint32_t N, uint32_t world, uint32_t wanted) {
 
 uint32_t sk_dp_flag_bytes(void) { return (uint32_t)(kFlagWordsPerLayer * sizeof(uint32_t)); }
 
-size_t sk_dp_scratch_bytes(uint32_t K, uint32_t N, uint32_t world) {
-    if (world == 0) return 0;
-    return ((((size_t)3 * N + 63) / 64) * 64 + (size_t)(K / world) * N) * sizeof(float);
-}
-
 int sk_dp_backward(sk_ctx *c, const sk_dense *const *layers, const sk_exchange *ex, uint32_t n, const void *target,
                    uint32_t target_rows, const void *x, uint32_t x_rows, uint32_t loss, uint32_t loss_act, float loss_leaky,
                    const sk_optim *lin, const sk_optim *nrm, uint32_t batch, uint32_t batch_stat, uint32_t world,
-                   uint32_t rank, uint32_t blocks, uint32_t epoch, float lr, float clamp, uint32_t step, float *scratch,
-                   size_t scratch_bytes) {
-    if (!c || !layers || !ex || !lin || !nrm || !target || !x || !scratch) return SK_ERR_NULL_POINTER;
-    if (reinterpret_cast<uintptr_t>(scratch) % 256 != 0) return fail(c, SK_ERR_NULL_POINTER, "scratch must be 256-byte aligned");
+                   uint32_t rank, uint32_t blocks, uint32_t epoch, float lr, float clamp, uint32_t step) {
+    if (!c || !layers || !ex || !lin || !nrm || !target || !x) return SK_ERR_NULL_POINTER;
     if (n == 0 || n > kDpMaxLayers) return fail(c, SK_ERR_INVALID_CONFIGURATION, "1 to %u layers", kDpMaxLayers);
     if (!(world == 2 || world == 4 || world == 8) || rank >= world)
         return fail(c, SK_ERR_INVALID_CONFIGURATION, "rank %u of %u ranks (2, 4 or 8)", rank, world);
-    if (blocks == 0) blocks = 4;
+    if (blocks == 0) blocks = 1;
     if (batch == 0 || batch_stat < batch) return fail(c, SK_ERR_INVALID_BATCH_SIZE, "local batch %u of %u rows", batch, batch_stat);
     if (!c->tc_err || !c->dp_counters) return fail(c, SK_ERR_DRIVER, "context has no device error word / counters");
     for (uint32_t i = 0; i < n; ++i) {
@@ -1247,7 +1160,7 @@ int sk_dp_backward(sk_ctx *c, const sk_dense *const *layers, const sk_exchange *
         if (rc) return rc;
         const sk_dense *L = layers[i];
         if (L->dtype == SK_F32 || L->dtype != layers[0]->dtype)
-            return fail(c, SK_ERR_INVALID_CONFIGURATION, "the pipelined exchange carries 16-bit blocks of one precision");
+            return fail(c, SK_ERR_INVALID_CONFIGURATION, "the native exchange carries 16-bit blocks of one precision");
         if (L->norm == SK_NORM_BATCH) return fail(c, SK_ERR_INVALID_CONFIGURATION, "BatchNorm blocks use the phased exchange");
         if (i > 0 && L->K != layers[i - 1]->N)
             return fail(c, SK_ERR_MISMATCHED_DIMENSIONS, "layer %u rows vs layer %u cols: expected %u, found %u", i, i - 1, layers[i - 1]->N, L->K);
@@ -1262,24 +1175,14 @@ int sk_dp_backward(sk_ctx *c, const sk_dense *const *layers, const sk_exchange *
                 reinterpret_cast<uintptr_t>(ex[i].peer_colsums[r]) % 16)
                 return fail(c, SK_ERR_NULL_POINTER, "exchange pointer of layer %u, rank %u is NULL or unaligned", i, r);
         if (ex[i].peer_w[rank] != L->w) return fail(c, SK_ERR_INVALID_CONFIGURATION, "layer %u: the weight tensor must be this rank's entry of peer_w", i);
-        if (sk_dp_scratch_bytes(L->K, L->N, world) > scratch_bytes)
-            return fail(c, SK_ERR_WORKSPACE, "layer %u needs %zu bytes of exchange scratch, %zu given", i,
-                        sk_dp_scratch_bytes(L->K, L->N, world), scratch_bytes);
     }
     if (cudaSetDevice(c->device) != cudaSuccess) return fail(c, SK_ERR_DRIVER, "cannot select device %d", c->device);
-    if (!c->comm_stream) {
-        int lo = 0, hi = 0;
-        cudaDeviceGetStreamPriorityRange(&lo, &hi);
-        if (cudaStreamCreateWithPriority(&c->comm_stream, cudaStreamNonBlocking, hi) != cudaSuccess ||
-            cudaEventCreateWithFlags(&c->comm_done, cudaEventDisableTiming) != cudaSuccess)
-            return fail(c, SK_ERR_DRIVER, "cannot create the exchange stream");
-    }
     c->fused_colsum_key = nullptr;
     return layers[0]->dtype == SK_F16
                ? dp_backward_impl<__half>(c, layers, ex, n, target, target_rows, x, x_rows, loss, loss_act, loss_leaky, lin, nrm,
-                                          batch, batch_stat, world, rank, blocks, epoch, lr, clamp, step, scratch)
+                                          batch, batch_stat, world, rank, blocks, epoch, lr, clamp, step)
                : dp_backward_impl<__nv_bfloat16>(c, layers, ex, n, target, target_rows, x, x_rows, loss, loss_act, loss_leaky,
-                                                 lin, nrm, batch, batch_stat, world, rank, blocks, epoch, lr, clamp, step, scratch);
+                                                 lin, nrm, batch, batch_stat, world, rank, blocks, epoch, lr, clamp, step);
 }
 
 int sk_peer_alloc(sk_ctx *c, size_t bytes, void **ptr, unsigned char handle_out[64]) {

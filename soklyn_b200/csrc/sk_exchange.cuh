@@ -1,28 +1,27 @@
-// Pipelined gradient exchange of the data-parallel backward pass (one process per GPU, buffers of
-// all ranks mapped into each other's address space). No counterpart in the reference, which is
-// single-device; the order it must keep is the reference's: a hidden delta reads the next layer's
-// weights AFTER their update (src/ffn.rs:141-163, src/io/device/ffn_device.rs:394-398).
+// Gradient exchange of the data-parallel backward pass (one process per GPU, buffers of all ranks
+// mapped into each other's address space). No counterpart in the reference, which is single-device;
+// the order it must keep is the reference's: a hidden delta reads the next layer's weights AFTER their
+// update (src/ffn.rs:141-163, src/io/device/ffn_device.rs:394-398).
 //
 // A weight matrix [K x N] is cut into `chunks` blocks of K/chunks rows; inside each block rank r owns
-// K/(chunks*world) rows. Per block, on every rank:
+// K/(chunks*world) rows. Per block, on every rank and all on the context's stream:
 //   1. the dW GEMM writes the block's rows of the local, averaged 16-bit gradient; flag A[block][r] is
 //      raised on every other rank (signal_chunk_kernel);
-//   2. reduce_rows_kernel (second stream, on the SMs the GEMMs leave free) waits for the other ranks'
-//      A[block] flags, pulls the rows this rank owns out of every rank's gradient buffer (peer loads over
-//      NVLink, many loads in flight per thread), adds them in rank order and writes the f32 sum locally
-//      (the reduce-scatter);
-//   3. the optimiser step of those rows runs on the main stream with every SM (it is bound by local HBM
-//      traffic, 32 bytes per parameter, which a few SMs cannot move): f32 master weights, moments, and
-//      the new 16-bit rows in the rank's own weight tensor;
-//   4. spread_rows_kernel (second stream) stores the new 16-bit rows into every other rank's weight tensor
-//      (peer stores) and raises flag B[block][r] there (the all-gather);
-//   5. the dX GEMM of the layer below waits, in its TMA producer, for the other ranks' B flags of just the
+//   2. exchange_update_kernel waits for the other ranks' A[block] flags and is then reduce-scatter +
+//      optimiser + all-gather in one kernel over every SM: it obtains the sum of the rows this rank owns
+//      (either by loading them from every rank's gradient buffer over NVLink and adding, or, when the arenas
+//      are bound to an NVSwitch multicast object, by ONE multimem.ld_reduce per 16 bytes: the switch adds),
+//      runs the optimiser step (f32 master weights, moments), and stores the new 16-bit rows into every
+//      rank's weight tensor (peer stores, or ONE multimem.st the switch delivers everywhere); the last
+//      thread block to finish raises flag B[block][r] on every other rank;
+//   3. the dX GEMM of the layer below waits, in its TMA producer, for the other ranks' B flags of just the
 //      blocks its tile needs.
-// Steps of one GPU are ordered by stream order and events only; the only in-kernel waits are for flags
-// that OTHER GPUs raise, every one bounded, ending in an error code instead of a hang, and a kernel whose
-// wait gave up (or that finds the error word set) changes nothing and raises no flag. The last block's
-// reduce kernel also adds the [3 x N] column sums of all ranks for the bias / normalisation-parameter step.
-// Flags hold the step's epoch number and only grow.
+// With multicast each GPU sends, per 67 M-parameter layer on 8 GPUs, 134 MB instead of 234 MB. The kernel of
+// the last block also adds the [3 x N] column sums of all ranks and steps bias and normalisation parameters
+// (identically on every rank). Work of one GPU is ordered by its stream; the only in-kernel waits are for
+// flags that OTHER GPUs raise, every one bounded, ending in an error code instead of a hang, and a kernel
+// whose wait gave up (or that finds the error word set) changes nothing and raises no flag. Flags hold the
+// step's epoch number and only grow.
 #pragma once
 
 #include "sk_rowwise.cuh"
@@ -30,7 +29,6 @@
 namespace sk {
 
 constexpr int kMaxChunks = 8;
-constexpr int kExchangeThreads = 512;
 // Flag words of one layer in a rank's arena: [2][kMaxChunks][kMaxRanks] (A = gradients ready, B = rows landed).
 constexpr int kFlagWordsPerLayer = 2 * kMaxChunks * kMaxRanks;
 enum : int { kErrExchangeFlags = 6 };
@@ -67,26 +65,55 @@ __global__ void wait_words_kernel(const uint32_t *flags, uint32_t chunks, uint32
     __threadfence_system();
 }
 
-struct ReduceArgs {
-    PeerPtrs grad, flags, colsums;   // per rank: gradient buffer, flag words, column sums of the layer
+// ---- NVSwitch multicast (NVLS) forms of the two transfers -------------------------------------------
+// With the arenas of all ranks bound to one multicast object, a load from the multicast address of the
+// gradient buffer is reduced inside the switch (each GPU then receives only the sum of the rows it owns),
+// and a store to the multicast address of the weight tensor lands in every GPU's copy (each GPU sends its
+// rows once). Per 67 M-parameter layer on 8 GPUs that is 134 MB per NVLink direction instead of 234 MB.
+// The switch adds the 16-bit partial gradients with f32 accumulation and returns the sum rounded to the
+// 16-bit type (the plain form keeps the f32 sum): one more rounding of 2^-11 (f16) on the summed gradient.
+template <typename T> __device__ __forceinline__ uint4 multimem_sum_16bit(const void *mc_addr);
+template <> __device__ __forceinline__ uint4 multimem_sum_16bit<__half>(const void *mc_addr) {
+    uint4 r;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc_addr) : "memory");
+    return r;
+}
+template <> __device__ __forceinline__ uint4 multimem_sum_16bit<__nv_bfloat16>(const void *mc_addr) {
+    uint4 r;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc_addr) : "memory");
+    return r;
+}
+__device__ __forceinline__ void multimem_store_16B(void *mc_addr, const uint4 &v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                 ::"l"(mc_addr), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+                   "f"(__uint_as_float(v.w)) : "memory");
+}
+
+template <typename T> struct ExchangeArgs {
+    PeerPtrs grad, w, flags, colsums;   // per rank: gradient buffer, weight tensor, flag words, column sums of the layer
+    const void *mc_grad;                // multicast addresses of the gradient buffers / weight tensors, or nullptr
+    void *mc_w;
     uint32_t world, rank, chunk, epoch;
-    size_t off, len;                 // elements: this rank's rows of this block inside the [K x N] matrix
-    float *sum;                      // local f32 [len]: the summed gradient of those rows
+    size_t off, len;                    // elements: this rank's rows of this block inside the [K x N] matrix
+    float *master, *dv, *dm;            // local f32 state, whole matrix
+    Optim opt;
+    Hyper hyp;                          // inv_m = 1: the staged gradients are already averaged
+    uint32_t *done;                     // local counter, zero between launches
     int *err;
-    uint32_t do_colsums, N;          // last block: also colsum_total[3 x N] = sum over ranks
-    float *colsum_total;
+    uint32_t do_vector, N;              // last block: also the bias / normalisation-parameter step
+    VectorParams<T> vp;
 };
 
-// Reduce-scatter of one block: U 16-byte runs per thread and rank are in flight together (W * U = 16).
-template <typename T, int W>
-__global__ void __launch_bounds__(kExchangeThreads, 1) reduce_rows_kernel(ReduceArgs a) {
-    extern __shared__ uint8_t sm_exclusive[];   // requested only to keep the SM to this block
+template <typename T, int W, bool MC>
+__global__ void __launch_bounds__(kRowThreads) exchange_update_kernel(ExchangeArgs<T> a) {
     __shared__ int ok_s;
-    constexpr int V = 8, U = 16 / W;
+    constexpr int V = 8;
     const uint32_t *my_flags = reinterpret_cast<const uint32_t *>(a.flags.p[a.rank]);
     if (threadIdx.x == 0) ok_s = *reinterpret_cast<volatile int *>(a.err) == 0;
     __syncthreads();
-    if (threadIdx.x < W && threadIdx.x != a.rank) {   // this rank's own gradient is ordered by an event
+    if (threadIdx.x < W && threadIdx.x != a.rank) {   // this rank's own gradient precedes the kernel on its stream
         if (!poll_flag_reached(my_flags + (0 * kMaxChunks + a.chunk) * kMaxRanks + threadIdx.x, a.epoch)) {
             ok_s = 0;
             atomicCAS(a.err, 0, kErrExchangeFlags);
@@ -97,79 +124,62 @@ __global__ void __launch_bounds__(kExchangeThreads, 1) reduce_rows_kernel(Reduce
     if (!ok_s) return;
 
     const size_t nvec = a.len / V, stride = (size_t)gridDim.x * blockDim.x;
-    const T *src[W];
+    float *master = a.master + a.off, *dv = a.dv + a.off, *dm = a.dm + a.off;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+        float g[V];
+        if (MC) {   // the switch adds the ranks' rows (f32 accumulation) and returns the sum in the 16-bit type
+            const uint4 r = multimem_sum_16bit<T>(reinterpret_cast<const T *>(a.mc_grad) + a.off + i * V);
+            const Pack<T, V> &pk = *reinterpret_cast<const Pack<T, V> *>(&r);
 #pragma unroll
-    for (int s = 0; s < W; ++s) src[s] = reinterpret_cast<const T *>(a.grad.p[s]) + a.off;
-    for (size_t base = (size_t)blockIdx.x * blockDim.x + threadIdx.x; base < nvec; base += stride * U) {
-        uint4 part[U][W];
+            for (int j = 0; j < V; ++j) g[j] = to_f32(pk.v[j]);
+        } else {
+            uint4 part[W];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const size_t i = base + (size_t)u * stride;
-            if (i < nvec) {
+            for (int s = 0; s < W; ++s)       // all loads in flight before the first use
+                part[s] = __ldcg(reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(a.grad.p[s]) + a.off + i * V));
 #pragma unroll
-                for (int s = 0; s < W; ++s) part[u][s] = __ldcg(reinterpret_cast<const uint4 *>(src[s] + i * V));
+            for (int j = 0; j < V; ++j) g[j] = 0.0f;
+#pragma unroll
+            for (int s = 0; s < W; ++s) {
+                const Pack<T, V> &pk = *reinterpret_cast<const Pack<T, V> *>(&part[s]);
+#pragma unroll
+                for (int j = 0; j < V; ++j) g[j] += to_f32(pk.v[j]);
             }
         }
+        float p[V], v[V], m[V];
+        load_run<float, V>(master + i * V, true, p);
+        load_run<float, V>(dv + i * V, true, v);
+        load_run<float, V>(dm + i * V, true, m);
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const size_t i = base + (size_t)u * stride;
-            if (i < nvec) {
-                float g[V];
+        for (int j = 0; j < V; ++j) p[j] = optimiser_step_fast(p[j], v[j], m[j], g[j] * kLossScaleInv, a.opt, a.hyp, true);
+        store_run<float, V>(dv + i * V, true, v);
+        store_run<float, V>(dm + i * V, true, m);
+        store_run<float, V>(master + i * V, true, p);
+        Pack<T, V> out;
 #pragma unroll
-                for (int j = 0; j < V; ++j) g[j] = 0.0f;
+        for (int j = 0; j < V; ++j) out.v[j] = from_f32<T>(p[j]);
+        const uint4 o = *reinterpret_cast<const uint4 *>(&out);
+        if (MC) {
+            multimem_store_16B(reinterpret_cast<T *>(a.mc_w) + a.off + i * V, o);   // lands in every rank's copy
+        } else {
 #pragma unroll
-                for (int s = 0; s < W; ++s) {
-                    const Pack<T, V> &pk = *reinterpret_cast<const Pack<T, V> *>(&part[u][s]);
-#pragma unroll
-                    for (int j = 0; j < V; ++j) g[j] += to_f32(pk.v[j]);
-                }
-                store_run<float, V>(a.sum + i * V, true, g);
-            }
+            for (int s = 0; s < W; ++s) *reinterpret_cast<uint4 *>(reinterpret_cast<T *>(a.w.p[s]) + a.off + i * V) = o;
         }
     }
-    if (a.do_colsums) {
-        for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < 3 * a.N; i += gridDim.x * blockDim.x) {
-            float t = 0.0f;
-#pragma unroll
-            for (int s = 0; s < W; ++s) t += __ldcg(reinterpret_cast<const float *>(a.colsums.p[s]) + i);
-            a.colsum_total[i] = t;
-        }
-    }
-}
 
-struct SpreadArgs {
-    PeerPtrs w, flags;               // per rank: weight tensor, flag words of the layer
-    uint32_t world, rank, chunk, epoch;
-    size_t off, len;                 // elements: this rank's rows of this block
-    uint32_t *done;                  // local counter, zero between launches
-    const int *err;
-};
-
-// All-gather of one block: this rank's new 16-bit rows into every other rank's weight tensor, then B[block][rank].
-template <typename T, int W>
-__global__ void __launch_bounds__(kExchangeThreads, 1) spread_rows_kernel(SpreadArgs a) {
-    extern __shared__ uint8_t sm_exclusive[];
-    constexpr int V = 8, U = 8;
-    if (*reinterpret_cast<const volatile int *>(a.err) != 0) return;   // an earlier wait gave up: publish nothing
-    const size_t nvec = a.len / V, stride = (size_t)gridDim.x * blockDim.x;
-    const T *mine = reinterpret_cast<const T *>(a.w.p[a.rank]) + a.off;
-    for (size_t base = (size_t)blockIdx.x * blockDim.x + threadIdx.x; base < nvec; base += stride * U) {
-        uint4 v[U];
+    if (a.do_vector) {   // column sums of all ranks, added in rank order, then the same step on every rank
+        for (uint32_t col = blockIdx.x * blockDim.x + threadIdx.x; col < a.N; col += gridDim.x * blockDim.x) {
+            float s3[3] = {0.0f, 0.0f, 0.0f};
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const size_t i = base + (size_t)u * stride;
-            if (i < nvec) v[u] = __ldcg(reinterpret_cast<const uint4 *>(mine + i * V));
-        }
+            for (int s = 0; s < W; ++s) {
+                const float *cs = reinterpret_cast<const float *>(a.colsums.p[s]);
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const size_t i = base + (size_t)u * stride;
-            if (i < nvec) {
-#pragma unroll
-                for (int s = 0; s < W; ++s)
-                    if ((uint32_t)s != a.rank) *reinterpret_cast<uint4 *>(reinterpret_cast<T *>(a.w.p[s]) + a.off + i * V) = v[u];
+                for (int w = 0; w < 3; ++w) s3[w] += __ldcg(cs + (size_t)w * a.N + col);
             }
+            vector_step<T>(a.vp, col, s3);
         }
     }
+
     // all stores of this block are out -> the last block to finish raises B[chunk][rank] on the other ranks
     __syncthreads();
     if (threadIdx.x == 0) {

@@ -214,18 +214,15 @@ class GpuContext:
                                              train_ctx.batch_size, train_ctx.learn_rate, train_ctx.grad_clamp,
                                              step & 0xFFFFFFFF))
 
-    # -- pipelined data-parallel backward: the whole pass in one native call --
+    # -- data-parallel backward: the whole pass in one native call --
     def dp_blocks(self, k: int, n: int, world: int, wanted: int) -> int:
         return int(self.lib.sk_dp_blocks(k, n, world, wanted))
 
     def dp_flag_bytes(self) -> int:
         return int(self.lib.sk_dp_flag_bytes())
 
-    def dp_scratch_bytes(self, k: int, n: int, world: int) -> int:
-        return int(self.lib.sk_dp_scratch_bytes(k, n, world))
-
     def gpu_dp_backward(self, layers, tables, target: Tensor, input: Tensor, loss_config, train_ctx, batch: int,
-                        batch_stat: int, world: int, rank: int, blocks: int, epoch: int, step: int, scratch: torch.Tensor):
+                        batch_stat: int, world: int, rank: int, blocks: int, epoch: int, step: int):
         n = len(layers)
         ptrs = (C.c_void_p * n)(*[C.addressof(l.desc()) for l in layers])
         lin = (SkOptim * n)(*[_optim(o) for o in train_ctx.optimisers])
@@ -234,8 +231,7 @@ class GpuContext:
         self._check(self.lib.sk_dp_backward(self.handle, ptrs, tables, n, target.ptr(), target.rows(), input.ptr(),
                                             input.rows(), loss_config.loss_func.value, act.ordinal(), act.coeff, lin, nrm,
                                             batch, batch_stat, world, rank, blocks, epoch & 0xFFFFFFFF,
-                                            train_ctx.learn_rate, train_ctx.grad_clamp, step & 0xFFFFFFFF,
-                                            scratch.data_ptr(), scratch.numel() * scratch.element_size()))
+                                            train_ctx.learn_rate, train_ctx.grad_clamp, step & 0xFFFFFFFF))
 
     # -- fused exchange over peer-mapped buffers (no counterpart in the reference) --
     def gpu_reduce_update_broadcast(self, layer, peer_grad, world: int, rank: int, peer_w, train_ctx, step: int):

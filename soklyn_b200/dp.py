@@ -28,13 +28,15 @@ Two exchange schemes:
   All flag waits are bounded (SK_ERR_DEVICE_TIMEOUT instead of a hang). Only the small column sums
   still use an NCCL all-reduce.
 
-* "pipelined" (default for 16-bit networks without BatchNorm on 2, 4 or 8 GPUs of one node): the fused
-  exchange cut into blocks of weight rows and run beside the GEMMs. The whole backward pass is ONE native
-  call (sk_dp_backward): per block of rows the dW GEMM writes the local gradient, a kernel on a second
-  stream (on SMs the GEMMs leave free) pulls, adds, steps and redistributes the rows this rank owns, and the
-  dX GEMM of the layer below waits inside its TMA producer only for the blocks its tile needs. Column sums
-  travel through the same arena; no library collective is left on the step. Inside block c of a matrix with
-  K rows, rank r owns rows [c*K/P + r*K/(P*W), c*K/P + (r+1)*K/(P*W)) (`owned_row_ranges(i)`).
+* "native" (default for 16-bit networks without BatchNorm on 2, 4 or 8 GPUs of one node): the fused
+  exchange with the whole backward pass sequenced in ONE native call (sk_dp_backward), optionally in P
+  blocks of weight rows: per block the dW GEMM writes the local gradient and raises a flag on the other
+  ranks, one kernel waits for their flags, sums, steps and redistributes the rows this rank owns, and the dX
+  GEMM of the layer below waits inside its TMA producer only for the blocks its tile needs. Column sums
+  travel through the same arena; no library collective and no host-side handshake is left on the step. With
+  `multicast` the arena lives in torch's symmetric memory and the kernel reduces inside the NVSwitch and
+  sends each row once. Inside block c of a matrix with K rows, rank r owns rows
+  [c*K/P + r*K/(P*W), c*K/P + (r+1)*K/(P*W)) (`owned_row_ranges(i)`).
 
 Under every sharded scheme a rank's f32 master weights and moments are current only for the rows it owns.
 `gather_state()` (collective) makes them complete on every rank; call it before saving a checkpoint or
@@ -90,11 +92,16 @@ def shard_rows(global_batch: int, rank: int, world: int):
 
 class DataParallelFFN:
     def __init__(self, context, network: FeedForwardNetwork, global_batch: int, rank: int, world: int, group=None,
-                 scheme: str = "auto", chunks: int = 0, collective_timeout: float | None = None):
+                 scheme: str = "auto", chunks: int = 0, collective_timeout: float | None = None, multicast=False):
         self.ctx, self.net, self.group = context, network, group
         self.rank, self.world, self.global_batch = rank, world, global_batch
         self.collective_timeout = collective_timeout
-        self.pipelined = False
+        # multicast (True / False / "auto"): put the exchange arena in torch's symmetric memory and, where the node
+        # has NVSwitch multicast, let the native exchange reduce inside the switch and send each row once; "auto"
+        # falls back to the library's own arenas when symmetric memory cannot be set up. Not for jobs in which a
+        # rank may leave while the others keep running.
+        self.multicast, self.mc_base, self._symm = multicast, 0, None
+        self.native = False
         self.blocks = []
         self.row_offset, self.local_batch = shard_rows(global_batch, rank, world)
         # BatchNorm takes its column statistics over the whole batch: its forward runs in three phases
@@ -127,27 +134,26 @@ class DataParallelFFN:
                 self.dw_shard.append(None)
         self.colsums = [torch.empty(3, l.get_weights().cols(), device=dev, dtype=torch.float32) for l in layers]
         self.collectives = 0
-        want = chunks if chunks > 0 else 4
-        can_pipeline = (world in (2, 4, 8) and hasattr(context, "gpu_dp_backward") and not self.bn_stats and bool(layers)
+        want = chunks if chunks > 0 else 1
+        can_native = (world in (2, 4, 8) and hasattr(context, "gpu_dp_backward") and not self.bn_stats and bool(layers)
                         and all(getattr(l, "precision", None) is not None and l.precision.value != 0 for l in layers)
                         and all(context.dp_blocks(l.get_weights().rows(), l.get_weights().cols(), world, want) > 0 for l in layers))
-        if scheme == "pipelined" and not can_pipeline:
-            raise log.InvalidConfiguration("the pipelined exchange needs 2, 4 or 8 ranks and 16-bit blocks without BatchNorm "
+        if scheme == "native" and not can_native:
+            raise log.InvalidConfiguration("the native exchange needs 2, 4 or 8 ranks and 16-bit blocks without BatchNorm "
                                            "whose rows split evenly")
-        self.pipelined = can_pipeline and scheme in ("auto", "pipelined")
-        self.fused = not self.pipelined and (scheme == "fused" or (scheme == "auto" and world > 1 and all(self.sharded)
+        self.native = can_native and scheme in ("auto", "native")
+        self.fused = not self.native and (scheme == "fused" or (scheme == "auto" and world > 1 and all(self.sharded)
                                                                    and world <= 8 and hasattr(context, "signal_peers")))
         self.epoch = 0
         if world > 1 and hasattr(context, "set_colsum_handover"):
             # backward() calls the delta of a layer and its weight-gradient GEMM back to back
             context.set_colsum_handover(True)
-        if self.pipelined:
+        if self.native:
             self.sharded = [True] * len(layers)
             self.blocks = [context.dp_blocks(l.get_weights().rows(), l.get_weights().cols(), world, want) for l in layers]
             self.want_blocks = want
-            need = max(context.dp_scratch_bytes(l.get_weights().rows(), l.get_weights().cols(), world) for l in layers)
-            self.scratch = torch.empty((need + 3) // 4, device=dev, dtype=torch.float32)   # summed gradient rows, column sums
-        if self.fused or self.pipelined:
+
+        if self.fused or self.native:
             self.dw, self.dw_shard = [], []      # these exchanges stage gradients in their own arena
             self._map_peers(layers)
 
@@ -167,10 +173,36 @@ class DataParallelFFN:
             off_colsums = off_flags + pad(flag_bytes)
             total = off_colsums + pad(3 * l.get_weights().cols() * 4)
             offsets.append((off_stage, off_recv, off_flags, nbytes, off_colsums))
-        self._arena, handle = self.ctx.peer_alloc(total)
-        table = [None] * W
-        dist.all_gather_object(table, handle, group=self.group)
-        self._bases = [self._arena if r == self.rank else self.ctx.peer_open(table[r]) for r in range(W)]
+        symm = None
+        if self.multicast:
+            # torch's symmetric memory: one allocation per rank, mapped into every rank and bound to a multicast object
+            try:
+                import torch.distributed._symmetric_memory as symm_mem
+                buf = symm_mem.empty(total, dtype=torch.uint8, device=self.ctx.device)
+                hdl = symm_mem.rendezvous(buf, self.group if self.group is not None else dist.group.WORLD)
+                symm = (buf, hdl)
+            except Exception:
+                if self.multicast != "auto":
+                    raise
+            # every rank must take the same road
+            ok = torch.tensor([1 if symm is not None else 0], device=self.ctx.device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+            if int(ok.item()) == 0:
+                symm = None
+        if symm is not None:
+            buf, hdl = symm
+            buf.zero_()
+            self._symm = symm
+            self._arena = buf.data_ptr()
+            self._bases = [int(p) for p in hdl.buffer_ptrs]
+            assert self._bases[self.rank] == self._arena, "symmetric memory: this rank's entry is not its own buffer"
+            self.mc_base = int(hdl.multicast_ptr) if hdl.multicast_ptr else 0
+        else:
+            self._arena, handle = self.ctx.peer_alloc(total)
+            table = [None] * W
+            dist.all_gather_object(table, handle, group=self.group)
+            self._bases = [self._arena if r == self.rank else self.ctx.peer_open(table[r]) for r in range(W)]
+        self._offsets = offsets
         arr = lambda off: (C.c_void_p * W)(*[b + off for b in self._bases])
         self.stage_ptr, self.recv_ptr, self.flag_ptr, self.nbytes = [], [], [], []
         self.p_stage, self.p_recv, self.p_flag_a, self.p_flag_b, self.p_colsums = [], [], [], [], []
@@ -200,7 +232,9 @@ class DataParallelFFN:
     def exchange_name(self) -> str:
         if self.world == 1:
             return "none"
-        return "pipelined" if self.pipelined else "fused" if self.fused else "nccl"
+        if self.native:
+            return "native+multicast" if self.mc_base else "native"
+        return "fused" if self.fused else "nccl"
 
     def _collective(self, fn, *args, **kwargs):
         """A library collective on the context's stream; with `collective_timeout` set it is waited for on
@@ -223,7 +257,7 @@ class DataParallelFFN:
     def owned_row_ranges(self, i: int):
         """[(first row, row count), ...] of layer i's weight matrix whose f32 masters and moments this rank keeps current."""
         k = self.net.get_layers()[i].get_weights().rows()
-        if self.world > 1 and self.pipelined:
+        if self.world > 1 and self.native:
             p = self.blocks[i]
             own = k // (p * self.world)
             return [(c * (k // p) + self.rank * own, own) for c in range(p)]
@@ -240,7 +274,7 @@ class DataParallelFFN:
         for i, layer in enumerate(self.net.get_layers()):
             if not self.sharded[i]:
                 continue
-            p = self.blocks[i] if self.pipelined else 1
+            p = self.blocks[i] if self.native else 1
             for t in (layer.get_master_weights(), layer.get_dv_weights(), layer.get_dm_weights()):
                 if t is None:
                     continue
@@ -267,11 +301,15 @@ class DataParallelFFN:
                 l.get_weights().data = own
                 l._desc = None
             torch.cuda.synchronize(self.ctx.device)
-            for r, b in enumerate(self._bases):
-                if r != self.rank:
-                    self.ctx.peer_close(b)
-            dist.barrier(group=self.group)
-            self.ctx.peer_free(self._arena)
+            if self._symm is None:
+                for r, b in enumerate(self._bases):
+                    if r != self.rank:
+                        self.ctx.peer_close(b)
+                dist.barrier(group=self.group)
+                self.ctx.peer_free(self._arena)
+            else:
+                dist.barrier(group=self.group)
+                self._symm = None
             self._bases = None
 
     def owned_rows(self, i: int):
@@ -318,10 +356,10 @@ class DataParallelFFN:
             return
         last = n - 1
         self.epoch += 1
-        if self.pipelined:
+        if self.native:
             self.net._check_backward(target, input, loss_config, _LocalBatch(train_ctx, self.local_batch))
             self.ctx.gpu_dp_backward(layers, self._exchange_tables(), target, input, loss_config, train_ctx, self.local_batch,
-                                     self.global_batch, self.world, self.rank, self.want_blocks, self.epoch, step, self.scratch)
+                                     self.global_batch, self.world, self.rank, self.want_blocks, self.epoch, step)
             return
         layers[last].compute_loss(self.ctx, target, loss_config)
         for i in range(last, -1, -1):
@@ -371,6 +409,9 @@ class DataParallelFFN:
                 tabs[i].peer_w = C.cast(self.p_recv[i], C.c_void_p)
                 tabs[i].peer_flags = C.cast(self.p_flag_a[i], C.c_void_p)
                 tabs[i].peer_colsums = C.cast(self.p_colsums[i], C.c_void_p)
+                if self.mc_base:
+                    off_stage, off_recv = self._offsets[i][0], self._offsets[i][1]
+                    tabs[i].mc_grad, tabs[i].mc_w = self.mc_base + off_stage, self.mc_base + off_recv
             self._tables = tabs
         return self._tables
 

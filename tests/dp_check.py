@@ -29,13 +29,13 @@ def main():
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     ctx = sk.GpuContext(16, local)
     steps = 3
-    specs = [(configs.scaled(configs.CONFIGS[4], dims=(256, 512, 256, 512, 256), batch=256, name="dp_pipelined_f16"), "pipelined"),
+    specs = [(configs.scaled(configs.CONFIGS[4], dims=(256, 512, 256, 512, 256), batch=256, name="dp_native_f16"), "native"),
              # per-rank batch above the row count from which the dX epilogue hands its column sums over, not a
              # multiple of the 32-row groups, with the statistics batch different from the local one
-             (configs.scaled(configs.CONFIGS[4], dims=(128, 256, 128, 256, 128), batch=1100 * world, name="dp_pipelined_tall_f16"), "pipelined"),
-             (configs.scaled(configs.CONFIGS[3], dims=(384, 256, 128, 16), batch=64 * world, name="dp_pipelined_layernorm_dropout_f16"), "pipelined"),
+             (configs.scaled(configs.CONFIGS[4], dims=(128, 256, 128, 256, 128), batch=1100 * world, name="dp_native_tall_f16"), "native"),
+             (configs.scaled(configs.CONFIGS[3], dims=(384, 256, 128, 16), batch=64 * world, name="dp_native_layernorm_dropout_f16"), "native"),
              # several tile columns per block of rows: the dX producer waits block by block
-             (configs.scaled(configs.CONFIGS[4], dims=(1024, 2048, 1024), batch=1024 * world, name="dp_pipelined_wide_f16"), "pipelined"),
+             (configs.scaled(configs.CONFIGS[4], dims=(1024, 2048, 1024), batch=1024 * world, name="dp_native_wide_f16"), "native"),
              (configs.scaled(configs.CONFIGS[4], dims=(128, 256, 128, 256, 128), batch=1100 * world, name="dp_fused_tall_f16"), "fused"),
              (configs.scaled(configs.CONFIGS[4], dims=(256, 512, 256, 512, 256), batch=256, name="dp_fused_f16"), "fused"),
              (configs.scaled(configs.CONFIGS[4], dims=(256, 512, 256, 512, 256), batch=256, name="dp_sharded_f16"), "sharded"),
@@ -49,13 +49,19 @@ def main():
                               ("silu", "silu", "identity"), (0.0, 0.0, 0.0), "f16", "mse", "identity", "adam", 1e-3, 128,
                               "xavier_normal", "normal", "normal"), "auto")]
     ok = True
-    for spec, scheme in specs:
+    # the native exchange again in four blocks of rows (the dX producer waits block by block), and with the
+    # arenas in symmetric memory (in-switch reduction and multicast stores where the node has them)
+    variants = [(spec, scheme, {}) for spec, scheme in specs]
+    variants += [(configs.scaled(spec, name=spec.name + "_blocks4"), "native", {"chunks": 4}) for spec, scheme in specs[:4]]
+    variants += [(configs.scaled(spec, name=spec.name + "_multicast"), "native", {"multicast": "auto", "chunks": c})
+                 for (spec, scheme), c in zip(specs[:4], (1, 4, 1, 4))]
+    for spec, scheme, extra in variants:
         w = configs.make_weights(spec)
         x, t, _ = configs.make_data(spec)
         per = spec.batch // world
         reset_tensor_ids(0)
         net = configs.build_network(ctx, spec, w, max_batch=per)
-        dp = DataParallelFFN(ctx, net, spec.batch, rank, world, scheme=scheme)
+        dp = DataParallelFFN(ctx, net, spec.batch, rank, world, scheme=scheme, **extra)
         xs = Tensor.from_cpu_vector(ctx, x[rank * per:(rank + 1) * per], (per, spec.dims[0]), spec.prec())
         ts = Tensor.from_cpu_vector(ctx, t[rank * per:(rank + 1) * per], (per, spec.dims[-1]), spec.prec())
         lrs = H.lr_schedule(spec, steps)

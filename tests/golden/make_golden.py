@@ -10,6 +10,8 @@ stride (at most ~160 values per tensor) plus its f64 sum and absolute sum.
 import os
 import sys
 
+from dataclasses import replace
+
 import numpy as np
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
@@ -22,7 +24,9 @@ from soklyn_b200.configs import CONFIGS, scaled  # noqa: E402
 
 def golden_specs():
     small3 = scaled(CONFIGS[3], dims=(384, 256, 128, 10), batch=96, precision="f32", name="classifier_small_f32")
-    small4 = scaled(CONFIGS[4], dims=(256, 512, 256, 512, 256), batch=192, precision="f32", name="wide_ffn_small_f32")
+    # the committed vectors of this network were taken with Adam at lr 1e-3 (at this size it trains at that rate)
+    small4 = replace(scaled(CONFIGS[4], dims=(256, 512, 256, 512, 256), batch=192, precision="f32", name="wide_ffn_small_f32"),
+                     lr=1e-3)
     odd = configs.NetSpec(9, "odd_shapes", (37, 50, 21, 7), ("batch", "rms", "disabled"),
                           ("tanh", "leaky:0.1", "identity"), (0.0, 0.3, 0.0), "f32", "mse", "sigmoid", "adam", 1e-3, 19,
                           "he_normal", "normal", "normal", True)

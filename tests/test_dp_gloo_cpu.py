@@ -226,8 +226,8 @@ def _gather_worker(rank, world, port, q):
     from soklyn_b200.ffn import FeedForwardNetwork
     layers = [_ShardedLayer(8, 3, 0, []), _ShardedLayer(4, 5, 1, [])]
     dp = DataParallelFFN(_Ctx(rank, []), FeedForwardNetwork(layers, 8), global_batch=8, rank=rank, world=world, scheme="sharded")
-    # pretend two blocks of rows per matrix, as the pipelined exchange lays them out
-    dp.pipelined, dp.blocks = True, [2, 1]
+    # pretend two blocks of rows per matrix, as the native exchange lays them out
+    dp.native, dp.blocks = True, [2, 1]
     for i, layer in enumerate(layers):
         for first, count in dp.owned_row_ranges(i):
             for t, scale in ((layer.master, 1.0), (layer.dv, 10.0), (layer.dm, 100.0)):

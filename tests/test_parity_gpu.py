@@ -304,3 +304,28 @@ def test_two_heads_on_one_trunk_match_oracle(gpu_ctx):
             assert H.relerr(got[name].reshape(ref[name].shape), ref[name]) <= 5e-4, f"block {i} {name}"
         for name in ("w", "b", "norm_w", "norm_b"):   # Adam: distance from the oracle in units of the largest rate
             assert np.abs(got[name].reshape(ref[name].shape) - ref[name]).max() <= 0.1 * 1e-3 * 4, f"block {i} {name}"
+
+
+@pytest.mark.parametrize("spec", [TALL4, TALL3], ids=lambda s: s.name)
+def test_lean_backward_gives_bit_identical_parameters(gpu_ctx, spec):
+    """SK_OPTION_LEAN_BACKWARD skips the stores of grad, the f32 d_prenorm, d_norm_w and d_norm_b in hidden
+    blocks whose column sums are taken in the dX epilogue. Nothing in the backward pass reads them, so three
+    training steps must leave every parameter, master copy and moment bit for bit as the default run does."""
+    w = configs.make_weights(spec)
+    x, t, _ = configs.make_data(spec)
+    dnet, dloss = H.run_device(gpu_ctx, spec, w, x, t, 3)
+    want = [H.device_state(gpu_ctx, l) for l in dnet.get_layers()]
+    try:
+        gpu_ctx.set_lean_backward(True)
+        lnet, lloss = H.run_device(gpu_ctx, spec, w, x, t, 3)
+        got = [H.device_state(gpu_ctx, l) for l in lnet.get_layers()]
+    finally:
+        gpu_ctx.set_lean_backward(False)
+    assert lloss == dloss
+    names = ("w", "b", "norm_w", "norm_b", "dv_w", "dm_w", "dv_b", "dm_b", "dv_nw", "dm_nw", "dv_nb", "dm_nb", "out", "mask")
+    for i, (a, b) in enumerate(zip(got, want)):
+        for name in names:
+            if name in a:
+                assert np.array_equal(a[name], b[name]), f"layer {i} {name} differs between the lean and the default run"
+    # and the skipped tensors really were skipped in the hidden blocks (they keep their initial zeros)
+    assert not np.any(got[0]["grad"]) and np.any(want[0]["grad"])
