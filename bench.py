@@ -225,6 +225,18 @@ def run_ours(args):
     ctx.profile_enable(False)
     # the e2e warm-up must leave slot parity consistent: step numbers continue from the warm-up
     ms_e2e = timed_steps(step_e2e, args.steps, 2, world, device)
+    # the same K steps once more with the lean backward option (not the headline: it leaves four API-visible
+    # gradient tensors of the hidden blocks unwritten), so that the line carries both
+    lean_ms = None
+    if world == 1 and spec.cfg == 4 and not args.lean:
+        ctx.set_lean_backward(True)
+        lean_ms = timed_steps(step_resident, args.steps, 2, world, device)
+        ctx.profile_enable(True)
+        for i in range(args.steps):
+            step_resident(10 ** 5 + i)
+        lean_prof = ctx.profile_read()
+        ctx.profile_enable(False)
+        ctx.set_lean_backward(False)
 
     # Correctness carried in the line: the loss of one more forward pass on the resident inputs (the
     # same host formula on every rank's rows, averaged), and under data parallelism the largest
@@ -285,6 +297,11 @@ def run_ours(args):
             "kernel_ms_per_step": {k: v[1] / args.steps for k, v in prof.items()},
             "loss_after": loss_after,
         }
+        if lean_ms is not None:
+            line["lean"] = {"ms_per_step": lean_ms / args.steps, "value": spec.batch / (lean_ms / args.steps * 1e-3), "unit": "samples/s",
+                            "gemm_dx_ms_per_step": lean_prof["gemm_dx"][1] / args.steps,
+                            "gemm_dx_tflops": flops["gemm_dx"] * args.steps / (lean_prof["gemm_dx"][1] * 1e-3) / 1e12,
+                            "note": "SK_OPTION_LEAN_BACKWARD: hidden blocks skip the stores of grad, f32 d_prenorm, d_norm_w, d_norm_b"}
         if world > 1:
             line["dp_check"] = {"max_abs_weight_diff_vs_rank0": w_diff, "loss_after": loss_after,
                                 "note": "every rank's 16-bit weights compared with rank 0's after the timed steps; "

@@ -608,7 +608,7 @@ int reduce_update_broadcast_impl(sk_ctx *c, const sk_dense *L, void *const *peer
     if (blocks < 1) blocks = 1;
     ProfScope ps(c, SK_PROF_UPDATE);
     reduce_update_broadcast_kernel<T><<<(uint32_t)blocks, kRowThreads, 0, c->stream>>>(
-        src, world, len, master_of<T>(L->master_w, L->w) + off, L->dv_w + off, L->dm_w + off, dst, lin, hyp);
+        src, world, len, master_of<T>(L->master_w, L->w) + off, L->dv_w + off, L->dm_w + off, dst, lin, hyp, c->tc_err);
     c->launches++;
     return check_cuda(c, cudaGetLastError(), "reduce + step + broadcast");
 }

@@ -575,8 +575,10 @@ __global__ void wait_flags_kernel(const uint32_t *flags, uint32_t world, uint32_
 template <typename T>
 __global__ void __launch_bounds__(kRowThreads)
 reduce_update_broadcast_kernel(PeerPtrs grad_rows, uint32_t world, size_t shard_len, float *master, float *dv,
-                               float *dm, PeerPtrs w_rows, Optim opt, Hyper hyp) {
+                               float *dm, PeerPtrs w_rows, Optim opt, Hyper hyp, const int *abort_flag) {
     constexpr int V = 8;
+    // the flag wait that precedes this kernel gave up: the other ranks' gradients are not complete, change nothing
+    if (abort_flag && *reinterpret_cast<const volatile int *>(abort_flag) != 0) return;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < shard_len / V; i += stride) {
         float g[V], p[V], v[V], m[V];
