@@ -125,45 +125,57 @@ __global__ void __launch_bounds__(kRowThreads) exchange_update_kernel(ExchangeAr
 
     const size_t nvec = a.len / V, stride = (size_t)gridDim.x * blockDim.x;
     float *master = a.master + a.off, *dv = a.dv + a.off, *dm = a.dm + a.off;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
-        float g[V];
-        if (MC) {   // the switch adds the ranks' rows (f32 accumulation) and returns the sum in the 16-bit type
-            const uint4 r = multimem_sum_16bit<T>(reinterpret_cast<const T *>(a.mc_grad) + a.off + i * V);
-            const Pack<T, V> &pk = *reinterpret_cast<const Pack<T, V> *>(&r);
+    // U runs of 16 bytes per thread and pass: their remote loads (the long latency: NVLink, and the switch's
+    // reduction with multicast) are all issued before the first is used; the local state of each run is then
+    // loaded, stepped and stored in turn.
+    constexpr int U = MC ? 4 : (W >= 8 ? 1 : 8 / W);
+    for (size_t base = (size_t)blockIdx.x * blockDim.x + threadIdx.x; base < nvec; base += stride * U) {
+        uint4 part[U][MC ? 1 : W];
 #pragma unroll
-            for (int j = 0; j < V; ++j) g[j] = to_f32(pk.v[j]);
-        } else {
-            uint4 part[W];
+        for (int u = 0; u < U; ++u) {
+            const size_t i = base + (size_t)u * stride;
+            if (i < nvec) {
+                if (MC) {   // the switch adds the ranks' rows (f32 accumulation) and returns the sum in the 16-bit type
+                    part[u][0] = multimem_sum_16bit<T>(reinterpret_cast<const T *>(a.mc_grad) + a.off + i * V);
+                } else {
 #pragma unroll
-            for (int s = 0; s < W; ++s)       // all loads in flight before the first use
-                part[s] = __ldcg(reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(a.grad.p[s]) + a.off + i * V));
+                    for (int s = 0; s < W; ++s)
+                        part[u][MC ? 0 : s] = __ldcg(reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(a.grad.p[s]) + a.off + i * V));
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const size_t i = base + (size_t)u * stride;
+            if (i >= nvec) continue;
+            float g[V];
 #pragma unroll
             for (int j = 0; j < V; ++j) g[j] = 0.0f;
 #pragma unroll
-            for (int s = 0; s < W; ++s) {
-                const Pack<T, V> &pk = *reinterpret_cast<const Pack<T, V> *>(&part[s]);
+            for (int s = 0; s < (MC ? 1 : W); ++s) {
+                const Pack<T, V> &pk = *reinterpret_cast<const Pack<T, V> *>(&part[u][s]);
 #pragma unroll
                 for (int j = 0; j < V; ++j) g[j] += to_f32(pk.v[j]);
             }
-        }
-        float p[V], v[V], m[V];
-        load_run<float, V>(master + i * V, true, p);
-        load_run<float, V>(dv + i * V, true, v);
-        load_run<float, V>(dm + i * V, true, m);
+            float p[V], v[V], m[V];
+            load_run<float, V>(master + i * V, true, p);
+            load_run<float, V>(dv + i * V, true, v);
+            load_run<float, V>(dm + i * V, true, m);
 #pragma unroll
-        for (int j = 0; j < V; ++j) p[j] = optimiser_step_fast(p[j], v[j], m[j], g[j] * kLossScaleInv, a.opt, a.hyp, true);
-        store_run<float, V>(dv + i * V, true, v);
-        store_run<float, V>(dm + i * V, true, m);
-        store_run<float, V>(master + i * V, true, p);
-        Pack<T, V> out;
+            for (int j = 0; j < V; ++j) p[j] = optimiser_step_fast(p[j], v[j], m[j], g[j] * kLossScaleInv, a.opt, a.hyp, true);
+            store_run<float, V>(dv + i * V, true, v);
+            store_run<float, V>(dm + i * V, true, m);
+            store_run<float, V>(master + i * V, true, p);
+            Pack<T, V> out;
 #pragma unroll
-        for (int j = 0; j < V; ++j) out.v[j] = from_f32<T>(p[j]);
-        const uint4 o = *reinterpret_cast<const uint4 *>(&out);
-        if (MC) {
-            multimem_store_16B(reinterpret_cast<T *>(a.mc_w) + a.off + i * V, o);   // lands in every rank's copy
-        } else {
+            for (int j = 0; j < V; ++j) out.v[j] = from_f32<T>(p[j]);
+            const uint4 o = *reinterpret_cast<const uint4 *>(&out);
+            if (MC) {
+                multimem_store_16B(reinterpret_cast<T *>(a.mc_w) + a.off + i * V, o);   // lands in every rank's copy
+            } else {
 #pragma unroll
-            for (int s = 0; s < W; ++s) *reinterpret_cast<uint4 *>(reinterpret_cast<T *>(a.w.p[s]) + a.off + i * V) = o;
+                for (int s = 0; s < W; ++s) *reinterpret_cast<uint4 *>(reinterpret_cast<T *>(a.w.p[s]) + a.off + i * V) = o;
+            }
         }
     }
 

@@ -297,9 +297,10 @@ output_error_kernel(T *__restrict__ out, const T *__restrict__ preact, const T *
 }
 
 // Output-layer delta without softmax: purely element-wise, 8 elements per thread with 128-bit
-// accesses (ffn/backward.cu:12-56). Requires N % 8 == 0 and 16-byte aligned tensors.
+// accesses (ffn/backward.cu:12-56). Requires N % 8 == 0 and 16-byte aligned tensors. Three blocks per SM
+// (80 registers): the kernel is bound by how many loads an SM keeps in flight.
 template <typename T>
-__global__ void __launch_bounds__(kRowThreads)
+__global__ void __launch_bounds__(kRowThreads, 3)
 output_error_elem_kernel(const T *__restrict__ out, const T *__restrict__ preact, const T *__restrict__ target,
                          const float *__restrict__ norm_w, float *__restrict__ grad, float *__restrict__ d_prenorm,
                          float *__restrict__ d_norm_w, float *__restrict__ d_norm_b, T *__restrict__ d_prenorm_lp,
