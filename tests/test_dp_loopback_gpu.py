@@ -83,7 +83,10 @@ def test_native_dp_backward_as_rank0_against_a_silent_peer(gpu_ctx, blocks):
             moved = np.abs(got["w"][own] - ref["w"][own]) / lr
             assert (moved > 0.1 * steps).mean() <= 0.01 and moved.max() <= 2.5 * steps, f"layer {i}: {moved.max():.2f} lr"
             assert np.array_equal(got["w"][~own], np.asarray(w[i], np.float32)[~own]), f"layer {i}: rows of the other rank changed"
-            assert H.relerr(got["out"], ref["out"]) <= 2e-3 and H.relerr(got["d_prenorm"], ref["d_prenorm"]) <= 1e-2
+            # the output block's delta is the plain run's; a hidden delta read the next layer's weights with only
+            # rank 0's rows stepped (each step moves a weight by about lr, a percent of its size here)
+            assert H.relerr(got["out"], ref["out"]) <= 2e-3
+            assert H.relerr(got["d_prenorm"], ref["d_prenorm"]) <= (2e-3 if i == len(layers) - 1 else 5e-2)
             assert np.abs(got["b"] - ref["b"]).max() <= 2.5 * lr and H.relerr(got["dm_b"] * 2, ref["dm_b"]) <= 1e-2
             # the owned rows of the 16-bit weights landed in the peer's weight tensor as well, the others did not
             mine = l.get_weights().data
