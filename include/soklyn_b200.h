@@ -110,8 +110,15 @@ int sk_ctx_set_stream(sk_ctx *ctx, void *stream);
  * 16-bit d_prenorm_lp. A deviation from the reference, whose getters expose those tensors
  * (src/mlp.rs:446-454): they keep stale contents. Parameters come out bit-identical. Off by default.
  * SK_OPTION_RESERVE_SMS: number of SMs the tensor-core GEMMs leave free, so that a kernel on another
- * stream can run beside them. 0 by default. */
-enum { SK_OPTION_GEMM_ENGINE = 0, SK_OPTION_COLSUM_HANDOVER = 1, SK_OPTION_LEAN_BACKWARD = 2, SK_OPTION_RESERVE_SMS = 3 };
+ * stream can run beside them. 0 by default.
+ * SK_OPTION_F32_TENSOR_CORES: 1 = f32 products large enough to pay for it (M*N*K >= 2^28, row pitches multiples
+ * of 8 elements) run on the tensor cores: both operands are split into three bf16 parts (8 + 8 + 8 significant
+ * bits) in the workspace and the six leading partial products are accumulated in f32 (src/cuda/kernel/math.cu:8-50
+ * is the FFMA loop this stands in for). Needs 6 bytes of workspace per operand element (sk_ctx_reserve); a
+ * product whose parts do not fit runs on the FFMA kernel. Results differ from the FFMA kernel's in the order
+ * and rounding of the f32 sums. Off by default. */
+enum { SK_OPTION_GEMM_ENGINE = 0, SK_OPTION_COLSUM_HANDOVER = 1, SK_OPTION_LEAN_BACKWARD = 2, SK_OPTION_RESERVE_SMS = 3,
+       SK_OPTION_F32_TENSOR_CORES = 4 };
 int sk_ctx_set_option(sk_ctx *ctx, uint32_t option, uint32_t value);
 /* Grow the scratch workspace; never called implicitly. */
 int sk_ctx_reserve(sk_ctx *ctx, size_t workspace_bytes);

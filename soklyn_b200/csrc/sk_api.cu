@@ -42,6 +42,10 @@ struct sk_ctx {
     bool lean = false;                     // SK_OPTION_LEAN_BACKWARD
     // data-parallel backward
     uint32_t *dp_counters = nullptr;       // one completion counter per (layer, block), zero between launches
+    // f32 GEMMs on the tensor cores (SK_OPTION_F32_TENSOR_CORES): device copies of the tensor maps of a launch
+    bool f32_tensor = false;
+    sk::TcSplitMaps *split_maps = nullptr; // ring of kSplitMapSlots entries
+    uint32_t split_slot = 0;
     // Column sums handed from the dX epilogue to the weight update of the same layer. Only inside
     // sk_ffn_backward (nothing can touch the tensors or the workspace in between there).
     bool in_ffn_backward = false;
@@ -58,6 +62,7 @@ struct sk_ctx {
 namespace {
 using namespace sk;
 
+constexpr uint32_t kSplitMapSlots = 16;
 constexpr uint32_t kDpMaxLayers = 64;
 constexpr uint32_t kDpCounterWords = kDpMaxLayers * kMaxChunks;
 
@@ -154,7 +159,7 @@ cudaError_t launch_tc_bn(sk_ctx *c, const CUtensorMap &ta, const CUtensorMap &tb
     const uint32_t sms = tc_sms(c);
     const uint32_t grid = tiles < sms ? tiles : sms;
     const uint32_t idesc = tc::make_instr_desc(std::is_same<T, __nv_bfloat16>::value ? 1u : 0u, A_MN, B_MN, kTcBM, BN);
-    kernel<<<grid, kTcThreads, S::kSmemBytes, c->stream>>>(ta, tb, M, N, K, idesc, group_n, epi, gate, c->tc_err);
+    kernel<<<grid, kTcThreads, S::kSmemBytes, c->stream>>>(ta, tb, M, N, K, idesc, group_n, epi, gate, c->tc_err, nullptr);
     c->tc_launches++;
     return cudaGetLastError();
 }
@@ -186,6 +191,84 @@ cudaError_t launch_gemm_tc(sk_ctx *c, uint32_t dtype, const T *A, size_t lda, co
                 : launch_tc_bn<T, A_MN, B_MN, 128, Epi>(c, ta, tb, M, N, K, epi, gate, group_n);
 }
 
+// ---- f32 operands on the tensor cores: three bf16 parts per operand, six partial products --------------
+// part[0] + part[1] + part[2] == x up to the last bit of f32 (each part holds the next 8 significant bits).
+__global__ void __launch_bounds__(256) split_bf16x3_kernel(const float *__restrict__ src, __nv_bfloat16 *__restrict__ p0,
+                                                            __nv_bfloat16 *__restrict__ p1, __nv_bfloat16 *__restrict__ p2,
+                                                            size_t len) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < len; i += stride) {
+        const float x = src[i];
+        const __nv_bfloat16 a = __float2bfloat16_rn(x);
+        const float r1 = x - __bfloat162float(a);
+        const __nv_bfloat16 b = __float2bfloat16_rn(r1);
+        const float r2 = r1 - __bfloat162float(b);
+        p0[i] = a; p1[i] = b; p2[i] = __float2bfloat16_rn(r2);
+    }
+}
+
+// Smallest shape worth the split passes, and what the split copies need of the workspace.
+inline bool split_worthwhile(uint32_t M, uint32_t N, uint32_t K) { return (double)M * N * K >= (double)(1u << 28); }
+
+template <bool A_MN, bool B_MN, class Epi>
+cudaError_t launch_gemm_tc_split(sk_ctx *c, const float *A, size_t lda, const float *B, size_t ldb, uint32_t M, uint32_t N,
+                                 uint32_t K, const Epi &epi, bool *taken) {
+    *taken = false;
+    if (!c->f32_tensor || c->cc_major != 10 || !c->encode_tiled || !c->tc_err || !c->split_maps) return cudaSuccess;
+    if (!split_worthwhile(M, N, K) || lda % 8 || ldb % 8 || reinterpret_cast<uintptr_t>(A) % 16 || reinterpret_cast<uintptr_t>(B) % 16)
+        return cudaSuccess;
+    // elements of the row-major sources the GEMM touches
+    const size_t len_a = (size_t)(A_MN ? K : M) * lda, len_b = (size_t)(B_MN ? K : N) * ldb;
+    const size_t pad = 128;   // elements: keeps every part 256-byte aligned
+    const size_t ea = (len_a + pad - 1) / pad * pad, eb = (len_b + pad - 1) / pad * pad;
+    if ((3 * ea + 3 * eb) * sizeof(__nv_bfloat16) > c->workspace_bytes) return cudaSuccess;
+    __nv_bfloat16 *base = (__nv_bfloat16 *)c->workspace;
+    __nv_bfloat16 *pa[3] = {base, base + ea, base + 2 * ea}, *pb[3] = {base + 3 * ea, base + 3 * ea + eb, base + 3 * ea + 2 * eb};
+    auto blocks = [&](size_t len) { size_t b = (len + 1023) / 1024; const size_t cap = (size_t)c->num_sms * 16; return (unsigned)(b > cap ? cap : b); };
+    split_bf16x3_kernel<<<blocks(len_a), 256, 0, c->stream>>>(A, pa[0], pa[1], pa[2], len_a);
+    split_bf16x3_kernel<<<blocks(len_b), 256, 0, c->stream>>>(B, pb[0], pb[1], pb[2], len_b);
+    c->launches += 2;
+    const uint32_t sms = tc_sms(c);
+    auto cost = [&](uint32_t bn) {
+        const uint64_t tiles = (uint64_t)((M + kTcBM - 1) / kTcBM) * ((N + bn - 1) / bn);
+        return ((tiles + sms - 1) / sms) * bn;
+    };
+    const bool wide = N > 128 && cost(256) * 4 <= cost(128) * 5;
+    const uint32_t bn = wide ? 256 : 128;
+    TcSplitMaps maps;
+    for (int i = 0; i < 3; ++i) {
+        const bool ok_a = A_MN ? get_tmap(c, pa[i], SK_BF16, M, K, lda, 64, &maps.a[i]) : get_tmap(c, pa[i], SK_BF16, K, M, lda, kTcBM, &maps.a[i]);
+        const bool ok_b = B_MN ? get_tmap(c, pb[i], SK_BF16, N, K, ldb, 64, &maps.b[i]) : get_tmap(c, pb[i], SK_BF16, K, N, ldb, bn, &maps.b[i]);
+        if (!ok_a || !ok_b) return cudaErrorInvalidValue;
+    }
+    TcSplitMaps *dev = c->split_maps + (c->split_slot++ % kSplitMapSlots);
+    cudaError_t e = cudaMemcpyAsync(dev, &maps, sizeof maps, cudaMemcpyHostToDevice, c->stream);
+    if (e != cudaSuccess) return e;
+    *taken = true;
+    const uint32_t tiles = ((M + kTcBM - 1) / kTcBM) * ((N + bn - 1) / bn);
+    const uint32_t grid = tiles < sms ? tiles : sms;
+    const uint32_t idesc = tc::make_instr_desc(1u, A_MN, B_MN, kTcBM, bn);
+    static uint64_t attr_set[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+    const unsigned d = (unsigned)c->device & 255u;
+    if (wide) {
+        auto kernel = gemm_tc_kernel<A_MN, B_MN, 256, Epi, true>;
+        if (!(attr_set[0][d >> 6] >> (d & 63) & 1ull)) {
+            if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TcShape<256>::kSmemBytes)) != cudaSuccess) return e;
+            attr_set[0][d >> 6] |= 1ull << (d & 63);
+        }
+        kernel<<<grid, kTcThreads, TcShape<256>::kSmemBytes, c->stream>>>(maps.a[0], maps.b[0], M, N, K, idesc, c->tc_group_n, epi, TcGate{}, c->tc_err, dev);
+    } else {
+        auto kernel = gemm_tc_kernel<A_MN, B_MN, 128, Epi, true>;
+        if (!(attr_set[1][d >> 6] >> (d & 63) & 1ull)) {
+            if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TcShape<128>::kSmemBytes)) != cudaSuccess) return e;
+            attr_set[1][d >> 6] |= 1ull << (d & 63);
+        }
+        kernel<<<grid, kTcThreads, TcShape<128>::kSmemBytes, c->stream>>>(maps.a[0], maps.b[0], M, N, K, idesc, c->tc_group_n, epi, TcGate{}, c->tc_err, dev);
+    }
+    c->tc_launches++;
+    return cudaGetLastError();
+}
+
 // Engine choice for one product of the DenseBlock path.
 template <typename TA, typename TB, bool A_KCONTIG, bool B_NCONTIG, class Epi>
 cudaError_t run_gemm(sk_ctx *c, uint32_t dtype, const TA *A, size_t lda, const TB *B, size_t ldb, uint32_t M, uint32_t N,
@@ -195,6 +278,11 @@ cudaError_t run_gemm(sk_ctx *c, uint32_t dtype, const TA *A, size_t lda, const T
             return launch_gemm_tc<TA, !A_KCONTIG, B_NCONTIG, Epi>(c, dtype, A, lda, B, ldb, M, N, K, epi, gate);
     }
     if (gate.flags) return cudaErrorNotSupported;   // only the tensor-core kernel can wait for rows in flight
+    if constexpr (std::is_same<TA, float>::value && std::is_same<TB, float>::value) {
+        bool taken = false;
+        const cudaError_t e = launch_gemm_tc_split<!A_KCONTIG, B_NCONTIG, Epi>(c, A, lda, B, ldb, M, N, K, epi, &taken);
+        if (taken || e != cudaSuccess) return e;
+    }
     return launch_gemm_simt<TA, TB, A_KCONTIG, B_NCONTIG, Epi>(c->stream, c->num_sms, A, lda, B, ldb, M, N, K, epi);
 }
 
@@ -804,12 +892,14 @@ int sk_ctx_create(int device, uint32_t tile_dim, void *stream, int create_stream
         if (cudaMalloc(&c->dp_counters, kDpCounterWords * sizeof(uint32_t)) == cudaSuccess)
             cudaMemset(c->dp_counters, 0, kDpCounterWords * sizeof(uint32_t));
         else c->dp_counters = nullptr;
+        if (cudaMalloc(&c->split_maps, kSplitMapSlots * sizeof(TcSplitMaps)) != cudaSuccess) c->split_maps = nullptr;
     }
     if (workspace_bytes == 0) workspace_bytes = (size_t)64 << 20;
     if (cudaMalloc(&c->workspace, workspace_bytes) != cudaSuccess) {
         if (c->own_stream) cudaStreamDestroy(c->stream);
         if (c->tc_err) cudaFree(c->tc_err);
         if (c->dp_counters) cudaFree(c->dp_counters);
+        if (c->split_maps) cudaFree(c->split_maps);
         delete c;
         return SK_ERR_DRIVER;
     }
@@ -825,6 +915,7 @@ void sk_ctx_destroy(sk_ctx *c) {
     if (c->workspace) cudaFree(c->workspace);
     if (c->tc_err) cudaFree(c->tc_err);
     if (c->dp_counters) cudaFree(c->dp_counters);
+    if (c->split_maps) cudaFree(c->split_maps);
     for (cudaEvent_t e : c->ev_pool) cudaEventDestroy(e);
     if (c->own_stream) cudaStreamDestroy(c->stream);
     delete c;
@@ -874,6 +965,7 @@ int sk_ctx_set_option(sk_ctx *c, uint32_t option, uint32_t value) {
         return SK_OK;
     }
     if (option == SK_OPTION_LEAN_BACKWARD && value <= 1) { c->lean = value != 0; return SK_OK; }
+    if (option == SK_OPTION_F32_TENSOR_CORES && value <= 1) { c->f32_tensor = value != 0; return SK_OK; }
     if (option == SK_OPTION_RESERVE_SMS && value < (uint32_t)c->num_sms) { c->reserve_sms = value; return SK_OK; }
     return fail(c, SK_ERR_INVALID_CONFIGURATION, "unknown option %u / value %u", option, value);
 }

@@ -15,7 +15,13 @@
 //   MN-major operand: element (mn, k) at ptr[k * ld + mn]  -> boxes {64 mn, 64 k}, 8 KiB apart
 // so forward (X K-major, W MN-major), dX (dY, W both K-major) and dW (X, dY both MN-major)
 // use the same kernel. Out-of-range parts of a box are zero-filled by TMA; the epilogue
-// clips rows and columns. Every barrier wait is bounded; on a timeout the kernel records an
+// clips rows and columns.
+//
+// f32 operands (SPLIT = true): each f32 matrix is split beforehand into three bf16 matrices a0 + a1 + a2
+// (8 significant bits each, 24 together), and the product is accumulated from the six partial products
+// whose weight is at least 2^-16 of the leading one, smallest first: a2.b0, a0.b2, a1.b1, a1.b0, a0.b1,
+// a0.b0. For every 64-deep K step the producer loads and the MMA thread multiplies the six pairs in turn
+// into the same f32 accumulator; everything else is the 16-bit kernel. Every barrier wait is bounded; on a timeout the kernel records an
 // error code and leaves.
 #pragma once
 
@@ -89,11 +95,18 @@ __device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uin
     ni = g * group_n + (r - mi * width);
 }
 
-template <bool A_MN, bool B_MN, int BN, class Epi>
+// Tensor maps of the three bf16 parts of both operands (SPLIT kernels only).
+struct TcSplitMaps { CUtensorMap a[3], b[3]; };
+constexpr int kSplitPairs = 6;
+__device__ __forceinline__ int split_a(int p) { return (0x001102 >> (4 * p)) & 0xF; }   // 2,0,1,1,0,0
+__device__ __forceinline__ int split_b(int p) { return (0x010120 >> (4 * p)) & 0xF; }   // 0,2,1,0,1,0
+
+template <bool A_MN, bool B_MN, int BN, class Epi, bool SPLIT = false>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                uint32_t M, uint32_t N, uint32_t K, uint32_t idesc, uint32_t group_n, Epi epi, TcGate gate,
-               int *err_flag) {
+               int *err_flag, const TcSplitMaps *split_maps) {
+    constexpr int NP = SPLIT ? kSplitPairs : 1;   // operand pairs multiplied per K step
     using S = TcShape<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -111,8 +124,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const uint32_t num_kb = (K + kTcBK - 1) / kTcBK;
 
     if (warp == 0 && lane == 0) {
-        tc::prefetch_tensormap(&tmap_a);
-        tc::prefetch_tensormap(&tmap_b);
+        if (SPLIT) {
+            for (int i = 0; i < 3; ++i) { tc::prefetch_tensormap(&split_maps->a[i]); tc::prefetch_tensormap(&split_maps->b[i]); }
+        } else {
+            tc::prefetch_tensormap(&tmap_a);
+            tc::prefetch_tensormap(&tmap_b);
+        }
         for (int s = 0; s < S::kStages; ++s) { tc::mbar_init(&full_bar[s], 1); tc::mbar_init(&empty_bar[s], 1); }
         for (int b = 0; b < 2; ++b) { tc::mbar_init(&tmem_full[b], 1); tc::mbar_init(&tmem_empty[b], kTcEpiWarps * 32); }
         tc::fence_barrier_init();
@@ -149,22 +166,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         tc::fence_proxy_async_all();   // the rows were written through the generic proxy, TMA reads them
                     }
                 }
-                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                for (uint32_t kp = 0; kp < num_kb * NP && ok; ++kp) {
+                    const uint32_t kb = kp / NP;
+                    const CUtensorMap *ma = SPLIT ? &split_maps->a[split_a(kp % NP)] : &tmap_a;
+                    const CUtensorMap *mb = SPLIT ? &split_maps->b[split_b(kp % NP)] : &tmap_b;
                     if (!tc::mbar_wait(&empty_bar[stage], phase ^ 1)) { ok = false; break; }
                     tc::mbar_arrive_expect_tx(&full_bar[stage], S::kStageBytes);
                     uint8_t *sa = stages + stage * S::kStageBytes, *sb = sa + kTcABytes;
                     const int32_t k0 = kb * kTcBK;
                     if (A_MN) {
 #pragma unroll
-                        for (int j = 0; j < kTcBM / 64; ++j) tc::tma_load_2d(sa + j * 8192, &tmap_a, &full_bar[stage], m0 + j * 64, k0);
+                        for (int j = 0; j < kTcBM / 64; ++j) tc::tma_load_2d(sa + j * 8192, ma, &full_bar[stage], m0 + j * 64, k0);
                     } else {
-                        tc::tma_load_2d(sa, &tmap_a, &full_bar[stage], k0, m0);
+                        tc::tma_load_2d(sa, ma, &full_bar[stage], k0, m0);
                     }
                     if (B_MN) {
 #pragma unroll
-                        for (int j = 0; j < BN / 64; ++j) tc::tma_load_2d(sb + j * 8192, &tmap_b, &full_bar[stage], n0 + j * 64, k0);
+                        for (int j = 0; j < BN / 64; ++j) tc::tma_load_2d(sb + j * 8192, mb, &full_bar[stage], n0 + j * 64, k0);
                     } else {
-                        tc::tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, n0);
+                        tc::tma_load_2d(sb, mb, &full_bar[stage], k0, n0);
                     }
                     if (++stage == S::kStages) { stage = 0; phase ^= 1; }
                 }
@@ -180,7 +200,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 if (!tc::mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) { ok = false; break; }
                 tc::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                for (uint32_t kb = 0; kb < num_kb * NP; ++kb) {   // with SPLIT: the six pairs of each K step in turn
                     if (!tc::mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
                     tc::tc_fence_after_sync();
                     const uint32_t sa = tc::smem_u32(stages + stage * S::kStageBytes), sb = sa + kTcABytes;

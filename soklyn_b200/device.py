@@ -81,6 +81,11 @@ class GpuContext:
         d_norm_w and d_norm_b (a documented deviation from the reference's API-visible tensors)."""
         self._check(self.lib.sk_ctx_set_option(self.handle, 2, int(on)))
 
+    def set_f32_tensor_cores(self, on: bool):
+        """Large f32 products on the tensor cores (three bf16 parts per operand, six partial products, f32
+        accumulation); needs 6 bytes of workspace per operand element (`reserve`)."""
+        self._check(self.lib.sk_ctx_set_option(self.handle, 4, int(on)))
+
     def set_reserve_sms(self, count: int):
         """SMs the tensor-core GEMMs leave free for a kernel on another stream."""
         self._check(self.lib.sk_ctx_set_option(self.handle, 3, int(count)))
