@@ -339,7 +339,11 @@ def gemm_sweep_rows(ctx, ms_list, kn_list, dtypes, peaks, index0: int = 0):
     acts = [sk.Activation.ReLU, sk.Activation.SiLU, sk.Activation.Tanh]
     rows, idx = [], index0
     for prec_name in dtypes:
-        prec = {"f16": sk.Precision.FP16, "f32": sk.Precision.FP32, "bf16": sk.Precision.BF16}[prec_name]
+        # "f32tc": f32 blocks with SK_OPTION_F32_TENSOR_CORES (three bf16 parts per operand in the workspace)
+        prec = {"f16": sk.Precision.FP16, "f32": sk.Precision.FP32, "f32tc": sk.Precision.FP32, "bf16": sk.Precision.BF16}[prec_name]
+        ctx.set_f32_tensor_cores(prec_name == "f32tc")
+        if prec_name == "f32tc":
+            ctx.reserve(6 * (max(ms_list) + max(kn_list)) * max(kn_list) + (1 << 20))
         for m in ms_list:
             for k in kn_list:
                 for n in kn_list:
@@ -360,7 +364,7 @@ def gemm_sweep_rows(ctx, ms_list, kn_list, dtypes, peaks, index0: int = 0):
                            "dX": lambda: ctx.gpu_hidden_layer_error(blk, nxt, m),
                            "dW": lambda: ctx.gpu_backward_pass(blk, x, tc, 1)}
                     rec = {"dtype": prec_name, "M": m, "K": k, "N": n, "act": act.ordinal()}
-                    heavy = float(m) * k * n >= 1e12 or (prec_name == "f32" and float(m) * k * n > 2e11)
+                    heavy = float(m) * k * n >= 1e12 or (prec_name.startswith("f32") and float(m) * k * n > 2e11)
                     for name, fn in ops.items():
                         for _ in range(1 if heavy else 3):
                             fn()
@@ -378,7 +382,8 @@ def gemm_sweep_rows(ctx, ms_list, kn_list, dtypes, peaks, index0: int = 0):
                     rows.append(rec)
                     del blk, nxt, x
                     torch.cuda.empty_cache()
-    sixteen = [r for r in rows if r["dtype"] != "f32"]
+    ctx.set_f32_tensor_cores(False)
+    sixteen = [r for r in rows if not r["dtype"].startswith("f32")]
     out = {"metric": "DenseBlock GEMM TFLOP/s", "unit": "TFLOP/s", "shapes": rows,
            "timing": "CUDA events around back-to-back calls of one entry point after warm-up; every call streams "
                      "operands and epilogue tensors larger than L2 for M >= 4096"}
@@ -400,7 +405,7 @@ def run_gemm_sweep(args):
     kn_list = [int(v) for v in args.sweep_kn.split(",")]
     res = gemm_sweep_rows(ctx, ms_list, kn_list, args.sweep_dtypes.split(","), peaks)
     rows = res["shapes"]
-    big = [r for r in rows if r["dtype"] != "f32" and r["M"] >= 4096]
+    big = [r for r in rows if not r["dtype"].startswith("f32") and r["M"] >= 4096]
     best = max((r["forward_tflops"] for r in big), default=0.0)
     mean = sum(r["forward_tflops"] + r["dX_tflops"] + r["dW_tflops"] for r in big) / max(1, 3 * len(big))
     f32 = [r for r in rows if r["dtype"] == "f32" and r["M"] >= 4096]
@@ -412,6 +417,9 @@ def run_gemm_sweep(args):
             "best_forward_tflops": best, "peak_burst": peaks["tflops_burst"], "peak_sustained": peaks["tflops_sustained"],
             "frac_burst": mean / peaks["tflops_burst"], "frac_sustained": mean / peaks["tflops_sustained"],
             "mean_f32_tflops": mean32, "sweep": rows}
+    f32tc = [r for r in rows if r["dtype"] == "f32tc" and r["M"] >= 4096]
+    if f32tc:
+        line["mean_f32_tensor_core_tflops"] = sum(r["forward_tflops"] + r["dX_tflops"] + r["dW_tflops"] for r in f32tc) / (3 * len(f32tc))
     print(json.dumps(line), flush=True)
     ctx.close()
 
@@ -507,7 +515,7 @@ def main():
                     help="gradient exchange of the data-parallel runs (see soklyn_b200/dp.py)")
     ap.add_argument("--sweep-m", default="256,1024,4096,16384,65536")
     ap.add_argument("--sweep-kn", default="1024,4096,8192")
-    ap.add_argument("--sweep-dtypes", default="f16,f32")
+    ap.add_argument("--sweep-dtypes", default="f16,f32", help="comma list of f16, bf16, f32, f32tc (f32 with the tensor-core option)")
     args = ap.parse_args()
     if args.config == 5 and args.impl != "reference":
         run_gemm_sweep(args)

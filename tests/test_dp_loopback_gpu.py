@@ -86,8 +86,10 @@ def test_native_dp_backward_as_rank0_against_a_silent_peer(gpu_ctx, blocks):
             # the output block's delta is the plain run's; a hidden delta read the next layer's weights with only
             # rank 0's rows stepped (each step moves a weight by about lr, a percent of its size here)
             assert H.relerr(got["out"], ref["out"]) <= 2e-3
-            assert H.relerr(got["d_prenorm"], ref["d_prenorm"]) <= (2e-3 if i == len(layers) - 1 else 5e-2)
-            assert np.abs(got["b"] - ref["b"]).max() <= 2.5 * lr and H.relerr(got["dm_b"] * 2, ref["dm_b"]) <= 1e-2
+            delta_tol = 2e-3 if i == len(layers) - 1 else 5e-2
+            assert H.relerr(got["d_prenorm"], ref["d_prenorm"]) <= delta_tol
+            # bias: summed over both ranks' column sums (the peer's are zero) and averaged over twice the batch
+            assert np.abs(got["b"] - ref["b"]).max() <= 2.5 * lr and H.relerr(got["dm_b"] * 2, ref["dm_b"]) <= delta_tol
             # the owned rows of the 16-bit weights landed in the peer's weight tensor as well, the others did not
             mine = l.get_weights().data
             peer = _alias_tensor(arenas[1] + off["w"], tuple(mine.shape), mine.dtype, gpu_ctx.device)
