@@ -200,22 +200,24 @@ def run_ours(args):
         outs = dp.forward(xd, spec.use_dropout, s)
         dp.backward(outs, td, xd, lc, tc, s)
 
-    out_host = torch.empty((local, spec.dims[-1]), dtype=tdt).pin_memory()
+    out_host = [torch.empty((local, spec.dims[-1]), dtype=tdt).pin_memory() for _ in range(2)]
     from soklyn_b200.pipeline import HostFeeder
     feeder = HostFeeder(ctx, [tuple(x_host.shape), tuple(t_host.shape)], prec)
     feeder.stage(1, [x_host, t_host])   # the first step (s = 1) reads slot 1
 
     def step_e2e(s):
-        # inputs of this step were staged from pinned host memory during the previous one; the
-        # next step's are staged now; the output goes back to the host while backward runs
+        # inputs of this step were staged from pinned host memory during the previous one; the next step's
+        # are staged now; the output goes back to the host while backward runs, into one of two host
+        # buffers, and the host waits for it only after the NEXT step has been queued (every step's result
+        # is read; the device never idles while the host waits)
         slot = s % 2
         xs, ts = feeder.acquire(slot)
         feeder.stage(1 - slot, [x_host, t_host])
         outs = dp.forward(xs, spec.use_dropout, s)
-        feeder.fetch(outs[-1], out_host, local)
+        feeder.fetch(outs[-1], out_host[slot], local, slot)
         dp.backward(outs, ts, xs, lc, tc, s)
         feeder.release(slot)
-        feeder.wait_output()                        # the step's result is on the host
+        feeder.wait_output(1 - slot)                # the previous step's result is on the host
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -296,7 +298,7 @@ def run_ours(args):
             "tflops_achieved": spec.flops_per_step() / (per_step * 1e-3) / 1e12,
             "e2e": {"value": spec.batch / (ms_e2e / args.steps * 1e-3), "unit": "samples/s",
                     "h2d_bytes_per_step": (x_host.numel() + t_host.numel()) * x_host.element_size(),
-                    "d2h_bytes_per_step": out_host.numel() * out_host.element_size()},
+                    "d2h_bytes_per_step": out_host[0].numel() * out_host[0].element_size()},
             "gpu_launches": int(launches),
             "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": peak,
@@ -343,7 +345,7 @@ def gemm_sweep_rows(ctx, ms_list, kn_list, dtypes, peaks, index0: int = 0):
         prec = {"f16": sk.Precision.FP16, "f32": sk.Precision.FP32, "f32tc": sk.Precision.FP32, "bf16": sk.Precision.BF16}[prec_name]
         ctx.set_f32_tensor_cores(prec_name == "f32tc")
         if prec_name == "f32tc":
-            ctx.reserve(6 * (max(ms_list) + max(kn_list)) * max(kn_list) + (1 << 20))
+            ctx.reserve(6 * 2 * max(max(ms_list), max(kn_list)) * max(kn_list) + (1 << 20))   # both operands of the largest product, three bf16 parts each
         for m in ms_list:
             for k in kn_list:
                 for n in kn_list:

@@ -25,7 +25,8 @@ class HostFeeder:
                        for s in shapes] for _ in range(slots)]
         self.ready = [torch.cuda.Event() for _ in range(slots)]
         self.consumed = [torch.cuda.Event() for _ in range(slots)]
-        self.out_done = torch.cuda.Event()
+        self.out_done = [torch.cuda.Event() for _ in range(slots)]
+        self._fetched = [False] * slots
         self.bytes_h2d = 0
         self.bytes_d2h = 0
         for e in self.consumed:
@@ -48,16 +49,20 @@ class HostFeeder:
     def release(self, slot: int):
         self.consumed[slot].record(self.ctx.stream)
 
-    def fetch(self, device_tensor: Tensor, host_out: torch.Tensor, rows: int):
+    def fetch(self, device_tensor: Tensor, host_out: torch.Tensor, rows: int, slot: int = 0):
         """Copy the first `rows` rows of a device tensor to pinned host memory behind the work
-        already queued on the context's stream; `wait_output()` blocks until it has landed."""
+        already queued on the context's stream; `wait_output(slot)` blocks until it has landed. With one
+        host buffer per slot the host can wait for step s's output while step s+1 is already queued."""
         produced = torch.cuda.Event()
         produced.record(self.ctx.stream)
         with torch.cuda.stream(self.copy_stream):
             self.copy_stream.wait_event(produced)
             host_out.copy_(device_tensor.data[:rows], non_blocking=True)
-            self.out_done.record(self.copy_stream)
+            self.out_done[slot].record(self.copy_stream)
+        self._fetched[slot] = True
         self.bytes_d2h += host_out.numel() * host_out.element_size()
 
-    def wait_output(self):
-        self.out_done.synchronize()
+    def wait_output(self, slot: int = 0):
+        if self._fetched[slot]:
+            self.out_done[slot].synchronize()
+            self._fetched[slot] = False
