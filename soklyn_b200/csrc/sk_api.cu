@@ -229,12 +229,7 @@ cudaError_t launch_gemm_tc_split(sk_ctx *c, const float *A, size_t lda, const fl
     split_bf16x3_kernel<<<blocks(len_b), 256, 0, c->stream>>>(B, pb[0], pb[1], pb[2], len_b);
     c->launches += 2;
     const uint32_t sms = tc_sms(c);
-    auto cost = [&](uint32_t bn) {
-        const uint64_t tiles = (uint64_t)((M + kTcBM - 1) / kTcBM) * ((N + bn - 1) / bn);
-        return ((tiles + sms - 1) / sms) * bn;
-    };
-    const bool wide = N > 128 && cost(256) * 4 <= cost(128) * 5;
-    const uint32_t bn = wide ? 256 : 128;
+    constexpr uint32_t bn = 128;   // the split kernel's tile: four accumulator buffers of 128 columns
     TcSplitMaps maps;
     for (int i = 0; i < 3; ++i) {
         const bool ok_a = A_MN ? get_tmap(c, pa[i], SK_BF16, M, K, lda, 64, &maps.a[i]) : get_tmap(c, pa[i], SK_BF16, K, M, lda, kTcBM, &maps.a[i]);
@@ -248,23 +243,14 @@ cudaError_t launch_gemm_tc_split(sk_ctx *c, const float *A, size_t lda, const fl
     const uint32_t tiles = ((M + kTcBM - 1) / kTcBM) * ((N + bn - 1) / bn);
     const uint32_t grid = tiles < sms ? tiles : sms;
     const uint32_t idesc = tc::make_instr_desc(1u, A_MN, B_MN, kTcBM, bn);
-    static uint64_t attr_set[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+    static uint64_t attr_set[4] = {0, 0, 0, 0};
     const unsigned d = (unsigned)c->device & 255u;
-    if (wide) {
-        auto kernel = gemm_tc_kernel<A_MN, B_MN, 256, Epi, true>;
-        if (!(attr_set[0][d >> 6] >> (d & 63) & 1ull)) {
-            if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TcShape<256>::kSmemBytes)) != cudaSuccess) return e;
-            attr_set[0][d >> 6] |= 1ull << (d & 63);
-        }
-        kernel<<<grid, kTcThreads, TcShape<256>::kSmemBytes, c->stream>>>(maps.a[0], maps.b[0], M, N, K, idesc, c->tc_group_n, epi, TcGate{}, c->tc_err, dev);
-    } else {
-        auto kernel = gemm_tc_kernel<A_MN, B_MN, 128, Epi, true>;
-        if (!(attr_set[1][d >> 6] >> (d & 63) & 1ull)) {
-            if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TcShape<128>::kSmemBytes)) != cudaSuccess) return e;
-            attr_set[1][d >> 6] |= 1ull << (d & 63);
-        }
-        kernel<<<grid, kTcThreads, TcShape<128>::kSmemBytes, c->stream>>>(maps.a[0], maps.b[0], M, N, K, idesc, c->tc_group_n, epi, TcGate{}, c->tc_err, dev);
+    auto kernel = gemm_tc_kernel<A_MN, B_MN, bn, Epi, true>;
+    if (!(attr_set[d >> 6] >> (d & 63) & 1ull)) {
+        if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TcShape<bn>::kSmemBytes)) != cudaSuccess) return e;
+        attr_set[d >> 6] |= 1ull << (d & 63);
     }
+    kernel<<<grid, kTcThreads, TcShape<bn>::kSmemBytes, c->stream>>>(maps.a[0], maps.b[0], M, N, K, idesc, c->tc_group_n, epi, TcGate{}, c->tc_err, dev);
     c->tc_launches++;
     return cudaGetLastError();
 }

@@ -130,13 +130,27 @@ gemm_simt_kernel(const TA *__restrict__ A, const TB *__restrict__ B, uint32_t M,
     }
 }
 
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+// acc.lo = a.lo * b.lo + acc.lo, acc.hi = a.hi * b.hi + acc.hi, each rounded to nearest like fmaf
+__device__ __forceinline__ void fma_f32x2(uint64_t &acc, uint64_t a, uint64_t b) {
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
+}
+
 // The same product for large problems: 128 x 128 x 16 tiles, two shared-memory buffers (the next
 // panel is stored while the current one is still being read: one barrier per 16-deep step), 128-bit
 // shared-memory reads, and an 8 x 8 register block per thread laid out as 2 x 2 groups of 4 x 4, 64
 // apart, so that the 16 threads of a row read 256 contiguous bytes of the B panel (no bank conflicts)
-// and the two rows of a warp read two broadcast addresses of the A panel. Two blocks per SM. The
-// summation order per output is the same increasing-k chain, so results equal the kernel above bit for
-// bit. The epilogue functor gets runs of 4 consecutive columns.
+// and the two rows of a warp read two broadcast addresses of the A panel. (A warp of 8 x 4 threads
+// needs a third fewer shared-memory wavefronts and measured 1 % slower.) Two blocks per SM. The summation order per output is the same increasing-k chain of fused
+// multiply-adds, so results equal the kernel above bit for bit. The epilogue functor gets runs of 4
+// consecutive columns.
 template <typename TA, typename TB, bool A_KCONTIG, bool B_NCONTIG, class Epi>
 __global__ void __launch_bounds__(kSimtThreads, 2)
 gemm_simt128_kernel(const TA *__restrict__ A, const TB *__restrict__ B, uint32_t M, uint32_t N, uint32_t K, size_t lda,
@@ -190,11 +204,14 @@ gemm_simt128_kernel(const TA *__restrict__ A, const TB *__restrict__ B, uint32_t
         }
     };
 
-    float acc[8][8];
+    // Accumulators as pairs of adjacent columns: one fma.rn.f32x2 (two round-to-nearest FMAs, the same
+    // arithmetic per element as fmaf) per pair halves the instructions issued per flop, which leaves the
+    // issue slots the shared-memory loads need.
+    uint64_t acc2[8][4];
 #pragma unroll
     for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+        for (int j = 0; j < 4; ++j) acc2[i][j] = 0ull;   // two +0.0f
 
     fetch(0);
     stage(0);
@@ -210,16 +227,23 @@ gemm_simt128_kernel(const TA *__restrict__ A, const TB *__restrict__ B, uint32_t
             const float4 b0 = *reinterpret_cast<const float4 *>(&Bs[buf][kk][tx * 4]);
             const float4 b1 = *reinterpret_cast<const float4 *>(&Bs[buf][kk][64 + tx * 4]);
             const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-            const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            const uint64_t b[4] = {pack_f32x2(b0.x, b0.y), pack_f32x2(b0.z, b0.w), pack_f32x2(b1.x, b1.y), pack_f32x2(b1.z, b1.w)};
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
+            for (int i = 0; i < 8; ++i) {
+                const uint64_t aa = pack_f32x2(a[i], a[i]);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                for (int j = 0; j < 4; ++j) fma_f32x2(acc2[i][j], aa, b[j]);
+            }
         }
         if (more) stage(buf ^ 1);
         __syncthreads();
         buf ^= 1;
     }
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) unpack_f32x2(acc2[i][j], acc[i][2 * j], acc[i][2 * j + 1]);
 
 #pragma unroll
     for (int i = 0; i < 8; ++i) {

@@ -44,7 +44,7 @@ template <int BN> struct TcShape {
     static constexpr int kStages = BN == 256 ? 4 : 6;
     static constexpr int kTmemCols = 2 * BN;                       // two accumulator buffers
     static constexpr int kEpiBufBytes = kTcEpiWarps * 32 * 33 * 4;
-    static constexpr int kBarBytes = (2 * kStages + 4) * 8 + 16;
+    static constexpr int kBarBytes = (2 * kStages + 8) * 8 + 16;   // room for four accumulator buffers (SPLIT)
     static constexpr int kSmemBytes = 1024 /*alignment slack*/ + kStages * kStageBytes + kEpiBufBytes + kBarBytes;
 };
 
@@ -96,8 +96,18 @@ __device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uin
 }
 
 // Tensor maps of the three bf16 parts of both operands (SPLIT kernels only).
+//
+// SPLIT kernels keep the running sum in registers, not in TMEM: the tensor pipe truncates (does not round)
+// when it adds into an f32 accumulator, one truncation per instruction, and over a long K that bias reaches
+// 1e-5 .. 1e-4 of the result. So the MMA warp closes an accumulator after every kSplitFlush K steps, the
+// epilogue warps add it to 64 registers per thread with round-to-nearest f32 adds, and four 128-column TMEM
+// buffers let the MMA warp run up to 4 * kSplitFlush K steps ahead of them (longer than a tile's epilogue,
+// which the same warps run). The tile is therefore 128 x 128. Inside one close the five small pairs of all
+// its K steps come first and the leading pair (part 0 x part 0) last: only those last 4 * kSplitFlush
+// instructions add into a sum of full magnitude, so the truncation bias stays below 1e-6 whatever K is.
 struct TcSplitMaps { CUtensorMap a[3], b[3]; };
 constexpr int kSplitPairs = 6;
+constexpr uint32_t kSplitFlush = 4;
 __device__ __forceinline__ int split_a(int p) { return (0x001102 >> (4 * p)) & 0xF; }   // 2,0,1,1,0,0
 __device__ __forceinline__ int split_b(int p) { return (0x010120 >> (4 * p)) & 0xF; }   // 0,2,1,0,1,0
 
@@ -107,6 +117,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                uint32_t M, uint32_t N, uint32_t K, uint32_t idesc, uint32_t group_n, Epi epi, TcGate gate,
                int *err_flag, const TcSplitMaps *split_maps) {
     constexpr int NP = SPLIT ? kSplitPairs : 1;   // operand pairs multiplied per K step
+    constexpr uint32_t kBufs = SPLIT ? 4 : 2;     // accumulator buffers in TMEM
+    static_assert(!SPLIT || BN == 128, "SPLIT kernels use four 128-column accumulator buffers");
+    constexpr uint32_t kTmemCols = kBufs * BN;
     using S = TcShape<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -115,8 +128,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + S::kStages * S::kStageBytes + S::kEpiBufBytes);
     uint64_t *empty_bar = full_bar + S::kStages;
     uint64_t *tmem_full = empty_bar + S::kStages;
-    uint64_t *tmem_empty = tmem_full + 2;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
+    uint64_t *tmem_empty = tmem_full + kBufs;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + kBufs);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t tiles_m = (M + kTcBM - 1) / kTcBM, tiles_n = (N + BN - 1) / BN;
@@ -131,11 +144,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             tc::prefetch_tensormap(&tmap_b);
         }
         for (int s = 0; s < S::kStages; ++s) { tc::mbar_init(&full_bar[s], 1); tc::mbar_init(&empty_bar[s], 1); }
-        for (int b = 0; b < 2; ++b) { tc::mbar_init(&tmem_full[b], 1); tc::mbar_init(&tmem_empty[b], kTcEpiWarps * 32); }
+        for (uint32_t b = 0; b < kBufs; ++b) { tc::mbar_init(&tmem_full[b], 1); tc::mbar_init(&tmem_empty[b], kTcEpiWarps * 32); }
         tc::fence_barrier_init();
     }
     if (warp == 1) {
-        tc::tmem_alloc(tmem_slot, S::kTmemCols);
+        tc::tmem_alloc(tmem_slot, kTmemCols);
         tc::tmem_relinquish();
     }
     tc::tc_fence_before_sync();
@@ -167,9 +180,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     }
                 }
                 for (uint32_t kp = 0; kp < num_kb * NP && ok; ++kp) {
-                    const uint32_t kb = kp / NP;
-                    const CUtensorMap *ma = SPLIT ? &split_maps->a[split_a(kp % NP)] : &tmap_a;
-                    const CUtensorMap *mb = SPLIT ? &split_maps->b[split_b(kp % NP)] : &tmap_b;
+                    uint32_t kb = kp, pair = 0;
+                    if constexpr (SPLIT) {   // order inside a close: small pairs of its K steps, then the leading pairs
+                        const uint32_t per = kSplitFlush * NP, kb0 = kp / per * kSplitFlush, s_in = kp % per;
+                        const uint32_t f = min(kSplitFlush, num_kb - kb0);
+                        if (s_in < (NP - 1) * f) { kb = kb0 + s_in / (NP - 1); pair = s_in % (NP - 1); }
+                        else { kb = kb0 + s_in - (NP - 1) * f; pair = NP - 1; }
+                    }
+                    const CUtensorMap *ma = SPLIT ? &split_maps->a[split_a(pair)] : &tmap_a;
+                    const CUtensorMap *mb = SPLIT ? &split_maps->b[split_b(pair)] : &tmap_b;
                     if (!tc::mbar_wait(&empty_bar[stage], phase ^ 1)) { ok = false; break; }
                     tc::mbar_arrive_expect_tx(&full_bar[stage], S::kStageBytes);
                     uint8_t *sa = stages + stage * S::kStageBytes, *sb = sa + kTcABytes;
@@ -196,28 +215,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (lane == 0) {
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
+            // An accumulator is closed once per tile, or (SPLIT) every kSplitFlush K steps: see TcSplitMaps.
+            const uint32_t closes = SPLIT ? (num_kb + kSplitFlush - 1) / kSplitFlush : 1u;
             for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                if (!tc::mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) { ok = false; break; }
-                tc::tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + acc * BN;
-                for (uint32_t kb = 0; kb < num_kb * NP; ++kb) {   // with SPLIT: the six pairs of each K step in turn
-                    if (!tc::mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
+                for (uint32_t cl = 0; cl < closes && ok; ++cl) {
+                    if (!tc::mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) { ok = false; break; }
                     tc::tc_fence_after_sync();
-                    const uint32_t sa = tc::smem_u32(stages + stage * S::kStageBytes), sb = sa + kTcABytes;
+                    const uint32_t d_tmem = tmem_base + acc * BN;
+                    const uint32_t steps = SPLIT ? min(kSplitFlush, num_kb - cl * kSplitFlush) * NP : num_kb;
+                    for (uint32_t st = 0; st < steps; ++st) {   // with SPLIT: the pairs of this close in the producer's order
+                        if (!tc::mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
+                        tc::tc_fence_after_sync();
+                        const uint32_t sa = tc::smem_u32(stages + stage * S::kStageBytes), sb = sa + kTcABytes;
 #pragma unroll
-                    for (int j = 0; j < kTcBK / 16; ++j) {
-                        const uint64_t da = A_MN ? tc::make_smem_desc(sa + j * 2048, 8192, 1024)
-                                                 : tc::make_smem_desc(sa + j * 32, 16, 1024);
-                        const uint64_t db = B_MN ? tc::make_smem_desc(sb + j * 2048, 8192, 1024)
-                                                 : tc::make_smem_desc(sb + j * 32, 16, 1024);
-                        tc::umma_f16(d_tmem, da, db, idesc, kb > 0 || j > 0);
+                        for (int j = 0; j < kTcBK / 16; ++j) {
+                            const uint64_t da = A_MN ? tc::make_smem_desc(sa + j * 2048, 8192, 1024)
+                                                     : tc::make_smem_desc(sa + j * 32, 16, 1024);
+                            const uint64_t db = B_MN ? tc::make_smem_desc(sb + j * 2048, 8192, 1024)
+                                                     : tc::make_smem_desc(sb + j * 32, 16, 1024);
+                            tc::umma_f16(d_tmem, da, db, idesc, st > 0 || j > 0);
+                        }
+                        tc::umma_commit(&empty_bar[stage]);      // stage reusable once these MMAs have read it
+                        if (++stage == S::kStages) { stage = 0; phase ^= 1; }
                     }
-                    tc::umma_commit(&empty_bar[stage]);      // stage reusable once these MMAs have read it
-                    if (++stage == S::kStages) { stage = 0; phase ^= 1; }
+                    if (!ok) break;
+                    tc::umma_commit(&tmem_full[acc]);            // accumulator complete
+                    if (++acc == kBufs) { acc = 0; acc_phase ^= 1; }
                 }
-                if (!ok) break;
-                tc::umma_commit(&tmem_full[acc]);            // accumulator complete
-                if ((acc ^= 1) == 0) acc_phase ^= 1;
             }
             if (!ok) atomicCAS(err_flag, 0, kTcErrMma);
         }
@@ -233,8 +257,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             uint32_t mi, ni;
             tile_coords(tile, tiles_m, tiles_n, group_n, mi, ni);
             const uint32_t m0 = mi * kTcBM, n0 = ni * BN;
-            if (!tc::mbar_wait(&tmem_full[acc], acc_phase)) { ok = false; break; }
-            tc::tc_fence_after_sync();
+            float part[2][32];                        // SPLIT: this thread's row, its 64 columns, summed over K
+            if constexpr (SPLIT) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) part[0][j] = part[1][j] = 0.0f;
+                for (uint32_t cl = 0; cl < (num_kb + kSplitFlush - 1) / kSplitFlush && ok; ++cl) {
+                    if (!tc::mbar_wait(&tmem_full[acc], acc_phase)) { ok = false; break; }
+                    tc::tc_fence_after_sync();
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        float t[32];
+                        tc::tmem_ld_32x32(tmem_base + ((quarter * 32) << 16) + acc * BN + half * (BN / 2) + h * 32, t);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) part[h][j] += t[j];
+                    }
+                    tc::tc_fence_before_sync();
+                    tc::mbar_arrive(&tmem_empty[acc]);
+                    if (++acc == kBufs) { acc = 0; acc_phase ^= 1; }
+                }
+                if (!ok) break;
+            } else {
+                if (!tc::mbar_wait(&tmem_full[acc], acc_phase)) { ok = false; break; }
+                tc::tc_fence_after_sync();
+            }
             // Runs of a 32-column chunk: pass p covers rows 8p + lane/4, columns 8*(lane%4) .. +8. The
             // fast path (128-bit accesses, a full run of 8 columns) keeps the global loads of the NEXT
             // group of G passes in flight while the current group is finished, also across chunks, so
@@ -267,7 +312,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         if (row_base + 8 * g < M) epi.prefetch(row_base + 8 * g, col, pre[0][g]);
                 }
                 float v[32];
-                tc::tmem_ld_32x32(tmem_base + ((quarter * 32) << 16) + acc * BN + c0, v);
+                if constexpr (SPLIT) {
+                    const bool first = c0 == half * (BN / 2);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = first ? part[0][j] : part[1][j];
+                } else {
+                    tc::tmem_ld_32x32(tmem_base + ((quarter * 32) << 16) + acc * BN + c0, v);
+                }
 #pragma unroll
                 for (int j = 0; j < 32; ++j) buf[lane * 33 + j] = v[j];
                 __syncwarp();
@@ -322,9 +373,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 have = have_n;
                 __syncwarp();
             }
-            tc::tc_fence_before_sync();
-            tc::mbar_arrive(&tmem_empty[acc]);
-            if ((acc ^= 1) == 0) acc_phase ^= 1;
+            if constexpr (!SPLIT) {
+                tc::tc_fence_before_sync();
+                tc::mbar_arrive(&tmem_empty[acc]);
+                if (++acc == kBufs) { acc = 0; acc_phase ^= 1; }
+            }
         }
         if (!ok && lane == 0) atomicCAS(err_flag, 0, kTcErrEpilogue);
     }
@@ -332,7 +385,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     tc::tc_fence_before_sync();
     __syncthreads();
     tc::tc_fence_after_sync();
-    if (warp == 1) tc::tmem_dealloc(tmem_base, S::kTmemCols);
+    if (warp == 1) tc::tmem_dealloc(tmem_base, kTmemCols);
 }
 
 } // namespace sk

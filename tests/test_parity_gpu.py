@@ -5,6 +5,7 @@ import numpy as np
 import pytest
 
 import harness as H
+import soklyn_b200 as sk
 from oracle import oracle as ok
 from soklyn_b200 import configs
 from soklyn_b200.configs import CONFIGS, scaled
@@ -331,12 +332,13 @@ def test_lean_backward_gives_bit_identical_parameters(gpu_ctx, spec):
     assert not np.any(got[0]["grad"]) and np.any(want[0]["grad"])
 
 
-def test_f32_tensor_core_option_stays_within_1e3_of_the_ffma_path(gpu_ctx):
+def test_f32_tensor_core_option_stays_within_5e5_of_the_ffma_path(gpu_ctx):
     """SK_OPTION_F32_TENSOR_CORES: large f32 products through three bf16 parts per operand and six partial
-    products on the tensor cores. The tensor pipe truncates its f32 accumulation (measured: the error of an
-    all-positive sum grows linearly with K, 2.6e-5 at K = 4096), so the option does not meet the 1e-5 of the
-    default FFMA path and is off by default; what it must meet is 1e-3 on every tensor, bit-equal dropout masks
-    and a loss within 1e-5."""
+    products on the tensor cores, summed over K in registers with round-to-nearest adds (the tensor pipe
+    truncates when it adds into its f32 accumulator, so an accumulator is closed every four 64-deep K steps).
+    Single products land within 3e-6 of the f32 oracle; through a LayerNorm backward that amplifies the
+    difference up to 1.4e-5, above the 1e-5 of the default FFMA path, so the option is off by default. What it
+    must meet: 5e-5 on every tensor, bit-equal dropout masks and a loss within 1e-5."""
     spec = scaled(CONFIGS[3], dims=(1024, 1024, 512, 16), batch=1024, precision="f32", name="f32_tensor_core_option")
     w = configs.make_weights(spec)
     x, t, _ = configs.make_data(spec)
@@ -360,6 +362,35 @@ def test_f32_tensor_core_option_stays_within_1e3_of_the_ffma_path(gpu_ctx):
             if name in a:
                 e = H.relerr(a[name], b[name])
                 worst = max(worst, e)
-                assert e <= 1e-3, f"layer {i} {name}: {e:.3e}"
+                assert e <= 5e-5, f"layer {i} {name}: {e:.3e}"
     assert worst > 0.0, "the tensor-core path did not run (results are bit-identical to the FFMA path)"
     assert launches >= plain_launches + 8      # the split kernels ran: two more launches per large product
+
+
+@pytest.mark.parametrize("k", [4096, 16384])
+def test_f32_tensor_core_option_has_no_truncation_bias_on_long_positive_sums(gpu_ctx, k):
+    """All-positive operands are the worst case for an accumulator that truncates: summed in TMEM alone the
+    error grew linearly with K (2.6e-5 of the result at K = 4096, 1.1e-4 at 16384). With the sum over K kept in
+    registers every element stays within 2e-6 of the float64 product at both depths."""
+    from soklyn_b200.configs import _GivenWeights
+    from soklyn_b200.core import Tensor
+    m = n = 512
+    rng = np.random.default_rng(5)
+    wt = rng.random((k, n), dtype=np.float32)
+    xv = rng.random((m, k), dtype=np.float32)
+    ref = xv.astype(np.float64) @ wt.astype(np.float64)
+    ref = ref / (1.0 + np.exp(-ref))              # SiLU; the products are in the hundreds, where it is the identity to 1e-40
+    cfg = sk.LayerInitConfig(sk.Normalisation.Disabled, sk.Activation.SiLU, sk.Regularisation.none(), 0.0)
+    try:
+        gpu_ctx.set_f32_tensor_cores(True)
+        gpu_ctx.reserve(6 * (m + n) * k * 2 + 4096)   # the three bf16 parts of both operands live in the workspace
+        blk = sk.DenseBlock(gpu_ctx, True, k, n, m, _GivenWeights(wt), cfg, sk.Precision.FP32)
+        xx = Tensor.from_cpu_vector(gpu_ctx, xv, (m, k), sk.Precision.FP32)
+        before = gpu_ctx.launch_count()
+        blk.forward(gpu_ctx, xx, m, False, 1)
+        assert gpu_ctx.launch_count() - before >= 3   # two split kernels and the product
+        got = H.device_state(gpu_ctx, blk)["out"].reshape(-1, n)[:m].astype(np.float64)
+    finally:
+        gpu_ctx.set_f32_tensor_cores(False)
+    rel = np.abs(got - ref) / np.abs(ref)
+    assert rel.max() <= 2e-6, f"K={k}: max relative error {rel.max():.2e}"
