@@ -113,10 +113,11 @@ int sk_ctx_set_stream(sk_ctx *ctx, void *stream);
  * stream can run beside them. 0 by default.
  * SK_OPTION_F32_TENSOR_CORES: 1 = f32 products large enough to pay for it (M*N*K >= 2^28, row pitches multiples
  * of 8 elements) run on the tensor cores: both operands are split into three bf16 parts (8 + 8 + 8 significant
- * bits) in the workspace and the six leading partial products are accumulated in f32 (src/cuda/kernel/math.cu:8-50
- * is the FFMA loop this stands in for). Needs 6 bytes of workspace per operand element (sk_ctx_reserve); a
+ * bits) in the workspace, the six leading partial products are multiplied on the tensor cores and summed over K
+ * in registers with round-to-nearest f32 adds, because the tensor pipe truncates when it adds into its own
+ * accumulator (src/cuda/kernel/math.cu:8-50 is the FFMA loop this stands in for). Needs 6 bytes of workspace per operand element (sk_ctx_reserve); a
  * product whose parts do not fit runs on the FFMA kernel. Results differ from the FFMA kernel's in the order
- * and rounding of the f32 sums. Off by default. */
+ * and rounding of the f32 sums: a single product by up to 3e-6 of its largest element. Off by default. */
 enum { SK_OPTION_GEMM_ENGINE = 0, SK_OPTION_COLSUM_HANDOVER = 1, SK_OPTION_LEAN_BACKWARD = 2, SK_OPTION_RESERVE_SMS = 3,
        SK_OPTION_F32_TENSOR_CORES = 4 };
 int sk_ctx_set_option(sk_ctx *ctx, uint32_t option, uint32_t value);

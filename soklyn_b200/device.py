@@ -82,8 +82,8 @@ class GpuContext:
         self._check(self.lib.sk_ctx_set_option(self.handle, 2, int(on)))
 
     def set_f32_tensor_cores(self, on: bool):
-        """Large f32 products on the tensor cores (three bf16 parts per operand, six partial products, f32
-        accumulation); needs 6 bytes of workspace per operand element (`reserve`)."""
+        """Large f32 products on the tensor cores (three bf16 parts per operand, six partial products, summed
+        over K in registers); needs 6 bytes of workspace per operand element (`reserve`)."""
         self._check(self.lib.sk_ctx_set_option(self.handle, 4, int(on)))
 
     def set_reserve_sms(self, count: int):
