@@ -196,9 +196,20 @@ def run_ours(args):
     tc = spec.train_context()
     lc = spec.loss_config()
 
-    def step_resident(s):
+    # Whole-step CUDA graphs for the launch-bound small networks (configs 1-3 on one GPU); the wide FFN's 23
+    # launches per 13 ms step gain nothing from them and stay kernel by kernel.
+    use_graph = world == 1 and (args.step_graph == "on" or (args.step_graph == "auto" and spec.cfg in (1, 2, 3)))
+
+    def step_eager(s):
         outs = dp.forward(xd, spec.use_dropout, s)
         dp.backward(outs, td, xd, lc, tc, s)
+
+    def step_resident(s):
+        if use_graph:
+            with ctx.step_graph(0):
+                step_eager(s)
+        else:
+            step_eager(s)
 
     out_host = [torch.empty((local, spec.dims[-1]), dtype=tdt).pin_memory() for _ in range(2)]
     from soklyn_b200.pipeline import HostFeeder
@@ -230,6 +241,7 @@ def run_ours(args):
     ms = timed_steps(step_resident, args.steps, args.warmup, world, device, before_timed=arm)
     launches = ctx.launch_count() - launches0[0]
     clocks = sampler.stop() if rank == 0 else None
+    eager_ms = timed_steps(step_eager, args.steps, 2, world, device) if use_graph else None
     # Per-kernel-class device times come from CUDA events around every launch; they are taken in a
     # second pass of the same K steps so that the event records stay out of the timed region.
     ctx.profile_enable(True)
@@ -292,7 +304,7 @@ def run_ours(args):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": spec.precision, "data": "synthetic (seeded N(0,1) inputs/targets, Xavier-uniform weights)",
             "config": {"workload": spec.name, "global_batch": spec.batch, "parallelism": f"dp{world}", "exchange": dp.exchange_name(),
-                       "params": spec.params(), "lean": bool(args.lean),
+                       "params": spec.params(), "lean": bool(args.lean), "step_graph": bool(use_graph),
                        "l2": "working set per step is far larger than L2 (126 MB)"},
             "tflops_per_step": spec.flops_per_step() / 1e12,
             "tflops_achieved": spec.flops_per_step() / (per_step * 1e-3) / 1e12,
@@ -311,6 +323,9 @@ def run_ours(args):
             "kernel_ms_per_step": {k: v[1] / args.steps for k, v in prof.items()},
             "loss_after": loss_after,
         }
+        if eager_ms is not None:
+            line["step_graph"] = {"ms_per_step": per_step, "kernel_by_kernel_ms_per_step": eager_ms / args.steps, **ctx.step_graph_stats(),
+                                  "note": "every step recorded by stream capture and launched as one graph (sk_step_begin / sk_step_end)"}
         if lean_ms is not None:
             line["lean"] = {"ms_per_step": lean_ms / args.steps, "value": spec.batch / (lean_ms / args.steps * 1e-3), "unit": "samples/s",
                             "gemm_dx_ms_per_step": lean_prof["gemm_dx"][1] / args.steps,
@@ -517,6 +532,8 @@ def main():
                     help="gradient exchange of the data-parallel runs (see soklyn_b200/dp.py)")
     ap.add_argument("--sweep-m", default="256,1024,4096,16384,65536")
     ap.add_argument("--sweep-kn", default="1024,4096,8192")
+    ap.add_argument("--step-graph", choices=["auto", "on", "off"], default="auto",
+                    help="launch each training step as one CUDA graph (auto: configs 1-3 on one GPU)")
     ap.add_argument("--sweep-dtypes", default="f16,f32", help="comma list of f16, bf16, f32, f32tc (f32 with the tensor-core option)")
     args = ap.parse_args()
     if args.config == 5 and args.impl != "reference":

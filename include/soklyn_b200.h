@@ -132,6 +132,28 @@ const char *sk_last_error(const sk_ctx *ctx);
 /* Number of kernels this context has launched since creation (for launch accounting). */
 uint64_t sk_launch_count(const sk_ctx *ctx);
 
+/* Whole-step graphs for the launch-bound small networks (no counterpart: the reference launches every kernel
+ * by itself and waits for it, src/io/device/ffn_device.rs:75,110,136). The sk_* calls a host makes between
+ * sk_step_begin and sk_step_end are recorded by CUDA stream capture (on a stream of the context's own, so the
+ * caller's may be the legacy default stream) instead of being launched one by one; sk_step_end turns the record
+ * into an executable graph and launches it on the context's stream. Every
+ * step is recorded afresh, so kernel arguments that change from step to step (the step number and Adam's bias
+ * corrections, the learning rate, the dropout seed, input pointers) need no care; when the sequence of kernels is
+ * the one of the slot's previous step, its executable graph is updated in place (cudaGraphExecUpdate), else it is
+ * instantiated anew. `slot` (< SK_STEP_SLOTS) names the executable graph to reuse: one per network or phase that
+ * alternates on the context. Results are those of the same calls made without the bracket, bit for bit.
+ * The first step of a slot runs unrecorded (first launches set function attributes and build tensor maps), and
+ * so does every step while profiling or SK_OPTION_F32_TENSOR_CORES is on. Between begin and end the host must
+ * not wait for the stream or read results: sk_sync, sk_profile_read, sk_ctx_reserve and sk_ctx_set_stream
+ * refuse with SK_ERR_INVALID_CONFIGURATION. If a call in between fails, sk_step_abort drops the record (nothing
+ * of the step has run then) and leaves the stream usable. sk_step_stats: out[0] graphs instantiated, out[1]
+ * updated in place, out[2] launched, out[3] steps that ran unrecorded. */
+enum { SK_STEP_SLOTS = 8 };
+int sk_step_begin(sk_ctx *ctx, uint32_t slot);
+int sk_step_end(sk_ctx *ctx);
+int sk_step_abort(sk_ctx *ctx);
+int sk_step_stats(const sk_ctx *ctx, uint64_t out[4]);
+
 /* Per-kernel-class device timing (no counterpart; the reference times phases on the host,
  * examples/mnist_train.rs:180-195). While enabled, every launch of the classes below is
  * bracketed by CUDA events on the context's stream; sk_profile_read waits for the stream and

@@ -430,6 +430,19 @@ class GpuContext {
     void synchronize() const { check(sk_sync(ctx_)); }
     uint64_t launch_count() const { return sk_launch_count(ctx_); }
     void reserve(size_t workspace_bytes) { check(sk_ctx_reserve(ctx_, workspace_bytes)); }
+    // One training step as one CUDA graph (sk_step_begin / sk_step_end): the calls made while the guard lives
+    // are recorded and launched together when it is closed. No counterpart in the reference.
+    class StepGraph {
+      public:
+        StepGraph(const GpuContext &c, uint32_t slot = 0) : c_(c) { c_.check(sk_step_begin(c_.ctx_, slot)); }
+        void launch() { open_ = false; c_.check(sk_step_end(c_.ctx_)); }   // throws on failure
+        ~StepGraph() { if (open_) sk_step_abort(c_.ctx_); }                // left by an exception: drop the record
+        StepGraph(const StepGraph &) = delete;
+        StepGraph &operator=(const StepGraph &) = delete;
+      private:
+        const GpuContext &c_;
+        bool open_ = true;
+    };
     // force the FFMA GEMM (true) or let the library use the tensor-core kernel where it can (false)
     void set_gemm_engine(bool ffma_only) { check(sk_ctx_set_option(ctx_, SK_OPTION_GEMM_ENGINE, ffma_only ? 1u : 0u)); }
 

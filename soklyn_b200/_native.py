@@ -104,6 +104,10 @@ _SIGS = {
     "sk_status_string": (C.c_char_p, [C.c_int]),
     "sk_last_error": (C.c_char_p, [C.c_void_p]),
     "sk_launch_count": (C.c_uint64, [C.c_void_p]),
+    "sk_step_begin": (C.c_int, [C.c_void_p, C.c_uint32]),
+    "sk_step_end": (C.c_int, [C.c_void_p]),
+    "sk_step_abort": (C.c_int, [C.c_void_p]),
+    "sk_step_stats": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint64)]),
     "sk_profile_enable": (C.c_int, [C.c_void_p, C.c_int]),
     "sk_profile_read": (C.c_int, [C.c_void_p, C.c_uint32, C.POINTER(C.c_uint64), C.POINTER(C.c_double)]),
     "sk_scramble_seed": (C.c_uint32, [C.c_uint32, C.c_uint32]),

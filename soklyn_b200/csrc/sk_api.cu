@@ -52,6 +52,14 @@ struct sk_ctx {
     bool colsum_handover = false;             // SK_OPTION_COLSUM_HANDOVER
     const void *fused_colsum_key = nullptr;   // d_prenorm of the layer whose partial sums sit in the workspace
     uint32_t fused_colsum_groups = 0, fused_colsum_batch = 0;
+    // whole-step graphs (sk_step_begin / sk_step_end)
+    struct StepGraph { cudaGraphExec_t exec = nullptr; bool warmed = false; };
+    StepGraph step_graphs[SK_STEP_SLOTS];
+    int step_open = -1;                    // slot between begin and end
+    bool step_capturing = false;
+    cudaStream_t record_stream = nullptr;  // the calls of a step are recorded on this stream (the legacy default stream
+    cudaStream_t user_stream = nullptr;    // cannot be captured); `stream` points here meanwhile, user_stream keeps the caller's
+    uint64_t step_stats[4] = {0, 0, 0, 0}; // instantiated, updated in place, launched, unrecorded steps
     // optional per-class event timing
     bool profiling = false;
     std::vector<cudaEvent_t> ev_pool;      // pairs: [2i] start, [2i+1] stop
@@ -74,6 +82,10 @@ int fail(sk_ctx *c, int code, const char *fmt, ...) {
         va_end(ap);
     }
     return code;
+}
+
+int step_recording(sk_ctx *c) {
+    return fail(c, SK_ERR_INVALID_CONFIGURATION, "not while a step graph is being recorded (sk_step_end or sk_step_abort first)");
 }
 
 int check_cuda(sk_ctx *c, cudaError_t e, const char *what) {
@@ -903,12 +915,15 @@ void sk_ctx_destroy(sk_ctx *c) {
     if (c->dp_counters) cudaFree(c->dp_counters);
     if (c->split_maps) cudaFree(c->split_maps);
     for (cudaEvent_t e : c->ev_pool) cudaEventDestroy(e);
+    for (auto &g : c->step_graphs) if (g.exec) cudaGraphExecDestroy(g.exec);
+    if (c->record_stream) cudaStreamDestroy(c->record_stream);
     if (c->own_stream) cudaStreamDestroy(c->stream);
     delete c;
 }
 
 int sk_ctx_set_stream(sk_ctx *c, void *stream) {
     if (!c) return SK_ERR_NULL_POINTER;
+    if (c->step_capturing) return step_recording(c);
     if (c->own_stream) { cudaStreamSynchronize(c->stream); cudaStreamDestroy(c->stream); c->own_stream = false; }
     c->stream = reinterpret_cast<cudaStream_t>(stream);
     return SK_OK;
@@ -916,6 +931,7 @@ int sk_ctx_set_stream(sk_ctx *c, void *stream) {
 
 int sk_ctx_reserve(sk_ctx *c, size_t workspace_bytes) {
     if (!c) return SK_ERR_NULL_POINTER;
+    if (c->step_capturing) return step_recording(c);
     c->fused_colsum_key = nullptr;   // column sums handed over by sk_hidden_error are for the very next call only
     if (workspace_bytes <= c->workspace_bytes) return SK_OK;
     cudaSetDevice(c->device);
@@ -931,6 +947,7 @@ int sk_ctx_reserve(sk_ctx *c, size_t workspace_bytes) {
 
 int sk_sync(sk_ctx *c) {
     if (!c) return SK_ERR_NULL_POINTER;
+    if (c->step_capturing) return step_recording(c);
     int rc = check_cuda(c, cudaStreamSynchronize(c->stream), "stream synchronize");
     if (rc || !c->tc_err || c->tc_launches == 0) return rc;
     int flag = 0;
@@ -942,8 +959,85 @@ int sk_sync(sk_ctx *c) {
     return SK_OK;
 }
 
+int sk_step_begin(sk_ctx *c, uint32_t slot) {
+    if (!c) return SK_ERR_NULL_POINTER;
+    if (slot >= SK_STEP_SLOTS) return fail(c, SK_ERR_INVALID_CONFIGURATION, "step slot %u (there are %d)", slot, (int)SK_STEP_SLOTS);
+    if (c->step_open >= 0) return fail(c, SK_ERR_INVALID_CONFIGURATION, "step slot %d is still open", c->step_open);
+    sk_ctx::StepGraph &g = c->step_graphs[slot];
+    const bool record = g.warmed && !c->profiling && !c->f32_tensor;
+    g.warmed = true;
+    if (record) {
+        cudaSetDevice(c->device);
+        int rc;
+        if (!c->record_stream && (rc = check_cuda(c, cudaStreamCreateWithFlags(&c->record_stream, cudaStreamNonBlocking), "create recording stream")))
+            return rc;
+        if ((rc = check_cuda(c, cudaStreamBeginCapture(c->record_stream, cudaStreamCaptureModeThreadLocal), "begin stream capture"))) return rc;
+        c->user_stream = c->stream;
+        c->stream = c->record_stream;
+    }
+    c->step_open = (int)slot;
+    c->step_capturing = record;
+    return SK_OK;
+}
+
+int sk_step_abort(sk_ctx *c) {
+    if (!c) return SK_ERR_NULL_POINTER;
+    if (c->step_open < 0) return SK_OK;
+    const bool recording = c->step_capturing;
+    c->step_open = -1;
+    c->step_capturing = false;
+    if (recording) {
+        cudaGraph_t graph = nullptr;
+        cudaStreamEndCapture(c->record_stream, &graph);   // an invalidated capture reports an error here and is over all the same
+        c->stream = c->user_stream;
+        if (graph) cudaGraphDestroy(graph);
+        cudaGetLastError();
+    }
+    return SK_OK;
+}
+
+int sk_step_end(sk_ctx *c) {
+    if (!c) return SK_ERR_NULL_POINTER;
+    if (c->step_open < 0) return fail(c, SK_ERR_INVALID_CONFIGURATION, "sk_step_end without sk_step_begin");
+    sk_ctx::StepGraph &g = c->step_graphs[c->step_open];
+    const bool recording = c->step_capturing;
+    c->step_open = -1;
+    c->step_capturing = false;
+    if (!recording) { c->step_stats[3]++; return SK_OK; }
+    cudaGraph_t graph = nullptr;
+    int rc = check_cuda(c, cudaStreamEndCapture(c->record_stream, &graph), "end stream capture");
+    c->stream = c->user_stream;
+    if (rc) { if (graph) cudaGraphDestroy(graph); cudaGetLastError(); return rc; }
+    if (g.exec) {
+        cudaGraphExecUpdateResultInfo info;
+        if (cudaGraphExecUpdate(g.exec, graph, &info) == cudaSuccess) {
+            c->step_stats[1]++;
+        } else {   // another sequence of kernels than the slot's last step
+            cudaGetLastError();
+            cudaGraphExecDestroy(g.exec);
+            g.exec = nullptr;
+        }
+    }
+    if (!g.exec) {
+        rc = check_cuda(c, cudaGraphInstantiate(&g.exec, graph, 0), "instantiate step graph");
+        if (rc) { g.exec = nullptr; cudaGraphDestroy(graph); return rc; }
+        c->step_stats[0]++;
+    }
+    cudaGraphDestroy(graph);
+    rc = check_cuda(c, cudaGraphLaunch(g.exec, c->stream), "launch step graph");
+    if (!rc) c->step_stats[2]++;
+    return rc;
+}
+
+int sk_step_stats(const sk_ctx *c, uint64_t out[4]) {
+    if (!c || !out) return SK_ERR_NULL_POINTER;
+    for (int i = 0; i < 4; ++i) out[i] = c->step_stats[i];
+    return SK_OK;
+}
+
 int sk_ctx_set_option(sk_ctx *c, uint32_t option, uint32_t value) {
     if (!c) return SK_ERR_NULL_POINTER;
+    if (c->step_capturing) return step_recording(c);
     if (option == SK_OPTION_GEMM_ENGINE && value <= 1) { c->gemm_engine = value; return SK_OK; }
     if (option == SK_OPTION_COLSUM_HANDOVER && value <= 1) {
         c->colsum_handover = value != 0;
@@ -980,6 +1074,7 @@ uint64_t sk_launch_count(const sk_ctx *c) { return c ? c->launches : 0; }
 
 int sk_profile_enable(sk_ctx *c, int on) {
     if (!c) return SK_ERR_NULL_POINTER;
+    if (c->step_capturing) return step_recording(c);
     c->profiling = on != 0;
     if (on) {
         c->ev_used = 0;
@@ -995,6 +1090,7 @@ int sk_profile_enable(sk_ctx *c, int on) {
 int sk_profile_read(sk_ctx *c, uint32_t cls, uint64_t *launches, double *total_ms) {
     if (!c || !launches || !total_ms) return SK_ERR_NULL_POINTER;
     if (cls >= SK_PROF_CLASSES) return fail(c, SK_ERR_INVALID_CONFIGURATION, "unknown kernel class %u", cls);
+    if (c->step_capturing) return step_recording(c);
     int rc = check_cuda(c, cudaStreamSynchronize(c->stream), "stream synchronize");
     if (rc) return rc;
     *launches = 0;

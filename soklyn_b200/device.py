@@ -7,6 +7,7 @@ methods do not block the host, `synchronize()` does.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes as C
 
 import torch
@@ -98,6 +99,25 @@ class GpuContext:
 
     def launch_count(self) -> int:
         return int(self.lib.sk_launch_count(self.handle))
+
+    @contextlib.contextmanager
+    def step_graph(self, slot: int = 0):
+        """Record the calls made inside the block (one training step: forward, backward) and launch them as one
+        CUDA graph when the block ends; results are those of the same calls made outside. For the small,
+        launch-bound networks. Inside the block nothing may wait for the stream or read a tensor back; the first
+        step of a slot runs unrecorded. `slot` names the executable graph that is reused from step to step."""
+        self._check(self.lib.sk_step_begin(self.handle, slot))
+        try:
+            yield
+        except BaseException:
+            self.lib.sk_step_abort(self.handle)
+            raise
+        self._check(self.lib.sk_step_end(self.handle))
+
+    def step_graph_stats(self) -> dict:
+        out = (C.c_uint64 * 4)()
+        self._check(self.lib.sk_step_stats(self.handle, out))
+        return dict(zip(("instantiated", "updated", "launched", "unrecorded"), (int(v) for v in out)))
 
     PROFILE_CLASSES = ("gemm_forward", "gemm_dx", "gemm_dw", "norm", "output_error", "colsum", "update", "exchange")
 
