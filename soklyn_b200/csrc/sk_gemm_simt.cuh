@@ -32,18 +32,20 @@ __device__ __forceinline__ void load_guarded(const T *p, int valid, bool vec_ok,
     }
 }
 
-template <typename TA, typename TB, bool A_KCONTIG, bool B_NCONTIG, int BM, int BN, int TM, int TN, class Epi>
+// BK: depth of one panel. These small tiles are used when the problem has few tiles (small or thin matrices),
+// where a block's time is one global-memory round trip per panel, not arithmetic: a deep panel (64 for the
+// 32 x 32 tile: eight elements per thread and operand in flight) divides the number of round trips.
+template <typename TA, typename TB, bool A_KCONTIG, bool B_NCONTIG, int BM, int BN, int TM, int TN, int BK, class Epi>
 __global__ void __launch_bounds__(kSimtThreads)
 gemm_simt_kernel(const TA *__restrict__ A, const TB *__restrict__ B, uint32_t M, uint32_t N, uint32_t K,
                  size_t lda, size_t ldb, bool a_vec, bool b_vec, Epi epi) {
-    constexpr int BK = kSimtBK;
     constexpr int EA = BM * BK / kSimtThreads; // elements of A per thread per panel
     constexpr int EB = BN * BK / kSimtThreads;
     static_assert((BM / TM) * (BN / TN) == kSimtThreads, "thread block must cover the tile");
     static_assert(EA >= 1 && EB >= 1 && BK % EA == 0 && BK % EB == 0, "panel split");
-    constexpr int PAD = 4;
-    __shared__ __align__(16) float As[BK][BM + PAD];
-    __shared__ __align__(16) float Bs[BK][BN + PAD];
+    constexpr int PAD = 1;   // odd row pitch: the column-wise stores of a K-contiguous operand spread over the banks
+    __shared__ float As[BK][BM + PAD];
+    __shared__ float Bs[BK][BN + PAD];
 
     const int t = threadIdx.x;
     const uint32_t m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -274,11 +276,11 @@ cudaError_t launch_gemm_simt(cudaStream_t stream, int num_sms, const TA *A, size
             <<<grid, kSimtThreads, 0, stream>>>(A, B, M, N, K, lda, ldb, a_vec, b_vec, epi);
     } else if (ctas(64, 64) >= (size_t)num_sms) {
         dim3 grid((N + 63) / 64, (M + 63) / 64);
-        gemm_simt_kernel<TA, TB, A_KCONTIG, B_NCONTIG, 64, 64, 4, 4, Epi>
+        gemm_simt_kernel<TA, TB, A_KCONTIG, B_NCONTIG, 64, 64, 4, 4, 32, Epi>
             <<<grid, kSimtThreads, 0, stream>>>(A, B, M, N, K, lda, ldb, a_vec, b_vec, epi);
     } else {
         dim3 grid((N + 31) / 32, (M + 31) / 32);
-        gemm_simt_kernel<TA, TB, A_KCONTIG, B_NCONTIG, 32, 32, 2, 2, Epi>
+        gemm_simt_kernel<TA, TB, A_KCONTIG, B_NCONTIG, 32, 32, 2, 2, 64, Epi>
             <<<grid, kSimtThreads, 0, stream>>>(A, B, M, N, K, lda, ldb, a_vec, b_vec, epi);
     }
     return cudaGetLastError();

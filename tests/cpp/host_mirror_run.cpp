@@ -9,7 +9,7 @@
 //                                        run through the Python mirror (bit for bit) and the CPU oracle.
 //
 // IN  (little endian): u32 magic 'SKLN', precision, layers, batch, max_batch, steps, loss, loss_act,
-//      optimiser (0 SGD, 1 Adam), use_dropout, fused (1: whole-network native calls), cosine (0/1),
+//      optimiser (0 SGD, 1 Adam), use_dropout, fused (bit 0: whole-network native calls, bit 1: every step as one CUDA graph), cosine (0/1),
 //      cosine_total, cosine_warmup; f32 lr, loss_act_coeff, cosine_min, cosine_max;
 //      u32 dims[layers+1]; per layer {u32 norm, u32 act, f32 act_coeff, f32 mask_coeff, u32 regu, f32 regu_coeff};
 //      f32 weights of every layer [K x N]; f32 x [batch x dims[0]]; f32 target [batch x dims[layers]].
@@ -250,9 +250,17 @@ int train(const char *in_path, const char *out_path) {
     Writer out(out_path);
     for (uint32_t s = 1; s <= steps; ++s) {
         if (cosine) tc.learn_rate = sched.step();
-        auto outs = net.forward(ctx, x, batch, use_dropout != 0, s, 0, fused != 0);
+        if (fused & 2u) {   // forward and backward recorded and launched as one graph; the output is read afterwards
+            GpuContext::StepGraph graph(ctx);
+            auto outs = net.forward(ctx, x, batch, use_dropout != 0, s, 0, (fused & 1u) != 0);
+            net.backward(ctx, outs, t, x, lc, tc, s, (fused & 1u) != 0);
+            graph.launch();
+            out.record("step_out", outs.back()->download(ctx));
+            continue;
+        }
+        auto outs = net.forward(ctx, x, batch, use_dropout != 0, s, 0, (fused & 1u) != 0);
         out.record("step_out", outs.back()->download(ctx));
-        net.backward(ctx, outs, t, x, lc, tc, s, fused != 0);
+        net.backward(ctx, outs, t, x, lc, tc, s, (fused & 1u) != 0);
     }
     ctx.synchronize();
     for (uint32_t i = 0; i < n_layers; ++i) {

@@ -23,6 +23,7 @@ MASTERS = {"w": ("get_master_weights", "get_weights"), "b": ("get_master_biases"
 
 
 def _cpp_train(tmp_path, spec, w, x, t, steps, fused):
+    # fused: bit 0 = whole-network native calls, bit 1 = every step recorded and launched as one CUDA graph
     src, dst = str(tmp_path / "in.bin"), str(tmp_path / f"out_{int(fused)}.bin")
     cpp_host.write_spec(src, spec, w, x, t, steps, fused=fused)
     r = cpp_host.run("train", src, dst)
@@ -41,6 +42,14 @@ def test_cpp_mirror_equals_python_mirror(gpu_ctx, tmp_path, spec, steps):
     # takes the column sums of a hidden layer in the dX epilogue (another summation order): parameters may
     # differ by rounding, within the rule the oracle comparison uses.
     assert [n for n, _ in recs] == [n for n, _ in unfused]
+    # GpuContext::StepGraph around every step: the same kernels with the same arguments, bit for bit. The
+    # per-step output record is left out: inside a recorded step nothing can be read back, so the driver reads
+    # it after backward, which has turned the output block's values into softmax / sigmoid of them in place.
+    graphed = _cpp_train(tmp_path, spec, w, x, t, steps, fused=3)
+    assert [n for n, _ in recs] == [n for n, _ in graphed]
+    for (name, a), (_, g) in zip(recs, graphed):
+        if name != "step_out":
+            assert np.array_equal(a, g, equal_nan=True), f"{name} differs under the step graph"
     lr_max = max(H.lr_schedule(spec, steps))
     for (name, a), (_, b) in zip(recs, unfused):
         kind = name.split(".")[-1]
