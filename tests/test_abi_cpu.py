@@ -46,6 +46,8 @@ def test_null_arguments_are_rejected_without_a_device():
     assert lib.sk_ctx_create(0, 16, None, 0, 0, None) == 9          # NULL out pointer
     assert lib.sk_dense_forward(None, None, None, 0, 0, 0, 0, 0) == 9
     assert lib.sk_sync(None) == 9
+    assert lib.sk_step_begin(None, 0) == 9 and lib.sk_step_end(None) == 9 and lib.sk_step_abort(None) == 9
+    assert lib.sk_step_stats(None, None) == 9
 
 
 def test_descriptor_layout_matches_header():
