@@ -434,6 +434,13 @@ def run_gemm_sweep(args):
             "best_forward_tflops": best, "peak_burst": peaks["tflops_burst"], "peak_sustained": peaks["tflops_sustained"],
             "frac_burst": mean / peaks["tflops_burst"], "frac_sustained": mean / peaks["tflops_sustained"],
             "mean_f32_tflops": mean32, "sweep": rows}
+    # the wide shapes (K, N >= 4096) apart: the narrow ones are bound by the epilogue's HBM traffic, not by the tensor pipe
+    wide = [r for r in big if r["K"] >= 4096 and r["N"] >= 4096]
+    if wide:
+        per = {k: sum(r[k + "_tflops"] for r in wide) / len(wide) for k in ("forward", "dX", "dW")}
+        wmean = sum(per.values()) / 3
+        line["wide_shapes"] = {"K_N_at_least": 4096, "mean_tflops": wmean, "frac_burst": wmean / peaks["tflops_burst"],
+                               "frac_sustained": wmean / peaks["tflops_sustained"], "per_class_tflops": per}
     f32tc = [r for r in rows if r["dtype"] == "f32tc" and r["M"] >= 4096]
     if f32tc:
         line["mean_f32_tensor_core_tflops"] = sum(r["forward_tflops"] + r["dX_tflops"] + r["dW_tflops"] for r in f32tc) / (3 * len(f32tc))
