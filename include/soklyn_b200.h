@@ -105,7 +105,7 @@ int sk_ctx_set_stream(sk_ctx *ctx, void *stream);
  * drops them). The caller promises not to modify those three tensors between the two calls. Off by
  * default; sk_ffn_backward always does this internally, where nothing can come in between.
  * SK_OPTION_LEAN_BACKWARD: 1 = a hidden block whose column sums are taken in the dX epilogue (16-bit,
- * batch > 1024, SiLU+RMSNorm or Mish+LayerNorm) does not store grad, the f32 d_prenorm, d_norm_w and
+ * batch >= 512, SiLU+RMSNorm or Mish+LayerNorm) does not store grad, the f32 d_prenorm, d_norm_w and
  * d_norm_b (src/mlp.rs:273-276): nothing in the backward pass reads them again, the GEMMs read the
  * 16-bit d_prenorm_lp. A deviation from the reference, whose getters expose those tensors
  * (src/mlp.rs:446-454): they keep stale contents. Parameters come out bit-identical. Off by default.

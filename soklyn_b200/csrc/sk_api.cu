@@ -38,6 +38,7 @@ struct sk_ctx {
     std::map<std::tuple<const void *, uint64_t, uint64_t, uint64_t, uint32_t, uint32_t>, CUtensorMap> tmaps;
     uint64_t tc_launches = 0;
     uint32_t tc_group_n = 8;               // tile columns walked together (SK_TC_GROUP_N at context creation)
+    uint32_t handover_min_rows = 0;        // column sums ride in the dX epilogue from this many rows on (SK_HANDOVER_MIN_ROWS at context creation)
     uint32_t reserve_sms = 0;              // SMs the tensor-core GEMMs leave free (for a concurrent exchange kernel)
     bool lean = false;                     // SK_OPTION_LEAN_BACKWARD
     // data-parallel backward
@@ -286,7 +287,7 @@ cudaError_t run_gemm(sk_ctx *c, uint32_t dtype, const TA *A, size_t lda, const T
 
 inline bool aligned16(const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
 constexpr uint32_t kSmallBatchRows = 256;   // up to here column sums and the vector step share one launch
-constexpr uint32_t kHandoverMinRows = 1024;  // below this a separate column-sum pass costs less than the heavier dX epilogue
+constexpr uint32_t kHandoverMinRows = 512;   // below this a separate column-sum pass costs as little as the heavier dX epilogue (measured: 0.4 % of a step gained at 512 rows, 1.4 % at 1024, none at 256)
 constexpr uint32_t kColsumFold = 8;   // slabs the per-32-row column sums of the dX epilogue are folded into
 
 Optim make_optim(const sk_optim *o, uint32_t step) {
@@ -453,7 +454,7 @@ int hidden_error_impl(sk_ctx *c, const sk_dense *cur, const sk_dense *next, uint
     c->fused_colsum_key = nullptr;
     const bool specialised = !f32 && ((cur->act == SK_ACT_SILU && cur->norm == SK_NORM_RMS) ||
                                       (cur->act == SK_ACT_MISH && cur->norm == SK_NORM_LAYER));
-    if ((c->in_ffn_backward || c->colsum_handover) && specialised && batch > kHandoverMinRows && epi.vec_ok && tc_eligible(c, cur->dtype, dy, ec, wn, ec)) {
+    if ((c->in_ffn_backward || c->colsum_handover) && specialised && batch >= c->handover_min_rows && epi.vec_ok && tc_eligible(c, cur->dtype, dy, ec, wn, ec)) {
         const uint32_t groups = (batch + 31) / 32;
         const size_t need = ((size_t)groups + kColsumFold) * 3 * cur->N * sizeof(float);
         if (need <= c->workspace_bytes) {
@@ -879,6 +880,8 @@ int sk_ctx_create(int device, uint32_t tile_dim, void *stream, int create_stream
     cudaFuncSetAttribute(sk::norm_rows_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
     c->cc_major = prop.major;
     if (const char *env = getenv("SK_TC_GROUP_N")) { const int v = atoi(env); if (v >= 1 && v <= 64) c->tc_group_n = (uint32_t)v; }
+    c->handover_min_rows = kHandoverMinRows;
+    if (const char *env = getenv("SK_HANDOVER_MIN_ROWS")) { const int v = atoi(env); if (v >= 32) c->handover_min_rows = (uint32_t)v; }
     {
         cudaDriverEntryPointQueryResult q;
         void *fn = nullptr;
