@@ -90,7 +90,9 @@ typedef struct {
  * ignore it. With create_stream != 0 the context creates (and owns) a non-blocking stream,
  * as the reference's GpuContext does; otherwise calls are ordered on the cudaStream_t
  * `stream`, where NULL is the legacy default stream. workspace_bytes of scratch are
- * allocated here (0 = default 64 MiB). */
+ * allocated here (0 = default 64 MiB). Two tuning values are read from the environment here: SK_TC_GROUP_N
+ * (tile columns the tensor-core kernels walk together, default 8) and SK_HANDOVER_MIN_ROWS (rows per call from
+ * which a hidden block's column sums are taken in the dX epilogue, default 512). */
 int sk_ctx_create(int device, uint32_t tile_dim, void *stream, int create_stream, size_t workspace_bytes,
                   sk_ctx **out);
 void sk_ctx_destroy(sk_ctx *ctx);
