@@ -20,8 +20,9 @@
 // f32 operands (SPLIT = true): each f32 matrix is split beforehand into three bf16 matrices a0 + a1 + a2
 // (8 significant bits each, 24 together), and the product is accumulated from the six partial products
 // whose weight is at least 2^-16 of the leading one, smallest first: a2.b0, a0.b2, a1.b1, a1.b0, a0.b1,
-// a0.b0. For every 64-deep K step the producer loads and the MMA thread multiplies the six pairs in turn
-// into the same f32 accumulator; everything else is the 16-bit kernel. Every barrier wait is bounded; on a timeout the kernel records an
+// a0.b0. For every 64-deep K step the producer loads the six part tiles once and the MMA thread multiplies
+// the six pairs in turn; the sum over K is finished in registers (see TcSplitMaps); everything else is the
+// 16-bit kernel. Every barrier wait is bounded; on a timeout the kernel records an
 // error code and leaves.
 #pragma once
 
@@ -44,7 +45,7 @@ template <int BN> struct TcShape {
     static constexpr int kStages = BN == 256 ? 4 : 6;
     static constexpr int kTmemCols = 2 * BN;                       // two accumulator buffers
     static constexpr int kEpiBufBytes = kTcEpiWarps * 32 * 33 * 4;
-    static constexpr int kBarBytes = (2 * kStages + 8) * 8 + 16;   // room for four accumulator buffers (SPLIT)
+    static constexpr int kBarBytes = (2 * kStages + 4) * 8 + 16;
     static constexpr int kSmemBytes = 1024 /*alignment slack*/ + kStages * kStageBytes + kEpiBufBytes + kBarBytes;
 };
 
@@ -99,15 +100,23 @@ __device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uin
 //
 // SPLIT kernels keep the running sum in registers, not in TMEM: the tensor pipe truncates (does not round)
 // when it adds into an f32 accumulator, one truncation per instruction, and over a long K that bias reaches
-// 1e-5 .. 1e-4 of the result. So the MMA warp closes an accumulator after every kSplitFlush K steps, the
-// epilogue warps add it to 64 registers per thread with round-to-nearest f32 adds, and four 128-column TMEM
-// buffers let the MMA warp run up to 4 * kSplitFlush K steps ahead of them (longer than a tile's epilogue,
-// which the same warps run). The tile is therefore 128 x 128. Inside one close the five small pairs of all
-// its K steps come first and the leading pair (part 0 x part 0) last: only those last 4 * kSplitFlush
-// instructions add into a sum of full magnitude, so the truncation bias stays below 1e-6 whatever K is.
+// 1e-5 .. 1e-4 of the result. So the MMA warp closes its accumulators after every kSplitFlush K steps and the
+// epilogue warps add them to 64 registers per thread with round-to-nearest f32 adds. A close has TWO
+// accumulators of 128 columns: the five small pairs go to one (its sum is 2^-8 of the result, so its
+// truncations do not count), the leading pair (part 0 x part 0) to the other, which therefore takes only
+// 4 * kSplitFlush = 32 instructions per close: the truncation bias is -7e-7 of the result whatever K is
+// (-3e-7 with 4 K steps per close, which left the MMA warp waiting behind the heavier epilogues). Two closes
+// fit TMEM, so the MMA warp runs up to 2 * kSplitFlush K steps ahead of the epilogue warps (about as long as
+// a tile's epilogue, which the same warps run). The tile is 128 x 128.
+// One pipeline stage of a SPLIT kernel holds one K step of ALL six part tiles (3 of A, 3 of B, 16 KiB each), so
+// every part is fetched once per K step and used by up to three of the six products; fetching per product
+// (twelve tiles per K step) left the tensor pipe 45 % busy, waiting for L2.
 struct TcSplitMaps { CUtensorMap a[3], b[3]; };
 constexpr int kSplitPairs = 6;
-constexpr uint32_t kSplitFlush = 4;
+constexpr uint32_t kSplitFlush = 8;
+constexpr uint32_t kSplitPartBytes = kTcBM * kTcBK * 2;          // one part tile: 128 x 64 bf16
+constexpr uint32_t kSplitStageBytes = 6 * kSplitPartBytes;      // A0 A1 A2 B0 B1 B2
+constexpr uint32_t kSplitStages = 2;
 __device__ __forceinline__ int split_a(int p) { return (0x001102 >> (4 * p)) & 0xF; }   // 2,0,1,1,0,0
 __device__ __forceinline__ int split_b(int p) { return (0x010120 >> (4 * p)) & 0xF; }   // 0,2,1,0,1,0
 
@@ -117,9 +126,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                uint32_t M, uint32_t N, uint32_t K, uint32_t idesc, uint32_t group_n, Epi epi, TcGate gate,
                int *err_flag, const TcSplitMaps *split_maps) {
     constexpr int NP = SPLIT ? kSplitPairs : 1;   // operand pairs multiplied per K step
-    constexpr uint32_t kBufs = SPLIT ? 4 : 2;     // accumulator buffers in TMEM
-    static_assert(!SPLIT || BN == 128, "SPLIT kernels use four 128-column accumulator buffers");
-    constexpr uint32_t kTmemCols = kBufs * BN;
+    constexpr uint32_t kBufs = 2;                 // accumulator buffers in TMEM (SPLIT: a buffer is a pair, small + leading)
+    constexpr uint32_t kBufCols = SPLIT ? 2 * BN : BN;
+    static_assert(!SPLIT || BN == 128, "SPLIT kernels use two pairs of 128-column accumulators");
+    static_assert(!SPLIT || kSplitStages * kSplitStageBytes <= (uint32_t)(TcShape<BN>::kStages * TcShape<BN>::kStageBytes), "SPLIT stages fit the ring");
+    constexpr uint32_t kTmemCols = kBufs * kBufCols;
     using S = TcShape<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -179,33 +190,50 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         tc::fence_proxy_async_all();   // the rows were written through the generic proxy, TMA reads them
                     }
                 }
-                for (uint32_t kp = 0; kp < num_kb * NP && ok; ++kp) {
-                    uint32_t kb = kp, pair = 0;
-                    if constexpr (SPLIT) {   // order inside a close: small pairs of its K steps, then the leading pairs
-                        const uint32_t per = kSplitFlush * NP, kb0 = kp / per * kSplitFlush, s_in = kp % per;
-                        const uint32_t f = min(kSplitFlush, num_kb - kb0);
-                        if (s_in < (NP - 1) * f) { kb = kb0 + s_in / (NP - 1); pair = s_in % (NP - 1); }
-                        else { kb = kb0 + s_in - (NP - 1) * f; pair = NP - 1; }
-                    }
-                    const CUtensorMap *ma = SPLIT ? &split_maps->a[split_a(pair)] : &tmap_a;
-                    const CUtensorMap *mb = SPLIT ? &split_maps->b[split_b(pair)] : &tmap_b;
-                    if (!tc::mbar_wait(&empty_bar[stage], phase ^ 1)) { ok = false; break; }
-                    tc::mbar_arrive_expect_tx(&full_bar[stage], S::kStageBytes);
-                    uint8_t *sa = stages + stage * S::kStageBytes, *sb = sa + kTcABytes;
-                    const int32_t k0 = kb * kTcBK;
-                    if (A_MN) {
+                if constexpr (SPLIT) {
+                    for (uint32_t kb = 0; kb < num_kb && ok; ++kb) {
+                        if (!tc::mbar_wait(&empty_bar[stage], phase ^ 1)) { ok = false; break; }
+                        tc::mbar_arrive_expect_tx(&full_bar[stage], kSplitStageBytes);
+                        uint8_t *base = stages + stage * kSplitStageBytes;
+                        const int32_t k0 = kb * kTcBK;
 #pragma unroll
-                        for (int j = 0; j < kTcBM / 64; ++j) tc::tma_load_2d(sa + j * 8192, ma, &full_bar[stage], m0 + j * 64, k0);
-                    } else {
-                        tc::tma_load_2d(sa, ma, &full_bar[stage], k0, m0);
-                    }
-                    if (B_MN) {
+                        for (int i = 0; i < 3; ++i) {
+                            uint8_t *sa = base + i * kSplitPartBytes, *sb = base + (3 + i) * kSplitPartBytes;
+                            if (A_MN) {
 #pragma unroll
-                        for (int j = 0; j < BN / 64; ++j) tc::tma_load_2d(sb + j * 8192, mb, &full_bar[stage], n0 + j * 64, k0);
-                    } else {
-                        tc::tma_load_2d(sb, mb, &full_bar[stage], k0, n0);
+                                for (int j = 0; j < kTcBM / 64; ++j) tc::tma_load_2d(sa + j * 8192, &split_maps->a[i], &full_bar[stage], m0 + j * 64, k0);
+                            } else {
+                                tc::tma_load_2d(sa, &split_maps->a[i], &full_bar[stage], k0, m0);
+                            }
+                            if (B_MN) {
+#pragma unroll
+                                for (int j = 0; j < BN / 64; ++j) tc::tma_load_2d(sb + j * 8192, &split_maps->b[i], &full_bar[stage], n0 + j * 64, k0);
+                            } else {
+                                tc::tma_load_2d(sb, &split_maps->b[i], &full_bar[stage], k0, n0);
+                            }
+                        }
+                        if (++stage == kSplitStages) { stage = 0; phase ^= 1; }
                     }
-                    if (++stage == S::kStages) { stage = 0; phase ^= 1; }
+                } else {
+                    for (uint32_t kb = 0; kb < num_kb && ok; ++kb) {
+                        if (!tc::mbar_wait(&empty_bar[stage], phase ^ 1)) { ok = false; break; }
+                        tc::mbar_arrive_expect_tx(&full_bar[stage], S::kStageBytes);
+                        uint8_t *sa = stages + stage * S::kStageBytes, *sb = sa + kTcABytes;
+                        const int32_t k0 = kb * kTcBK;
+                        if (A_MN) {
+#pragma unroll
+                            for (int j = 0; j < kTcBM / 64; ++j) tc::tma_load_2d(sa + j * 8192, &tmap_a, &full_bar[stage], m0 + j * 64, k0);
+                        } else {
+                            tc::tma_load_2d(sa, &tmap_a, &full_bar[stage], k0, m0);
+                        }
+                        if (B_MN) {
+#pragma unroll
+                            for (int j = 0; j < BN / 64; ++j) tc::tma_load_2d(sb + j * 8192, &tmap_b, &full_bar[stage], n0 + j * 64, k0);
+                        } else {
+                            tc::tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, n0);
+                        }
+                        if (++stage == S::kStages) { stage = 0; phase ^= 1; }
+                    }
                 }
             }
             if (!ok) atomicCAS(err_flag, 0, gate_ok ? kTcErrProducer : kTcErrGate);
@@ -221,22 +249,46 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 for (uint32_t cl = 0; cl < closes && ok; ++cl) {
                     if (!tc::mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) { ok = false; break; }
                     tc::tc_fence_after_sync();
-                    const uint32_t d_tmem = tmem_base + acc * BN;
-                    const uint32_t steps = SPLIT ? min(kSplitFlush, num_kb - cl * kSplitFlush) * NP : num_kb;
-                    for (uint32_t st = 0; st < steps; ++st) {   // with SPLIT: the pairs of this close in the producer's order
-                        if (!tc::mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
-                        tc::tc_fence_after_sync();
-                        const uint32_t sa = tc::smem_u32(stages + stage * S::kStageBytes), sb = sa + kTcABytes;
+                    const uint32_t d_tmem = tmem_base + acc * kBufCols;
+                    if constexpr (SPLIT) {
+                        const uint32_t d_small = d_tmem, d_lead = d_tmem + BN;
+                        const uint32_t steps = min(kSplitFlush, num_kb - cl * kSplitFlush);
+                        for (uint32_t st = 0; st < steps; ++st) {
+                            if (!tc::mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
+                            tc::tc_fence_after_sync();
+                            const uint32_t base = tc::smem_u32(stages + stage * kSplitStageBytes);
 #pragma unroll
-                        for (int j = 0; j < kTcBK / 16; ++j) {
-                            const uint64_t da = A_MN ? tc::make_smem_desc(sa + j * 2048, 8192, 1024)
-                                                     : tc::make_smem_desc(sa + j * 32, 16, 1024);
-                            const uint64_t db = B_MN ? tc::make_smem_desc(sb + j * 2048, 8192, 1024)
-                                                     : tc::make_smem_desc(sb + j * 32, 16, 1024);
-                            tc::umma_f16(d_tmem, da, db, idesc, st > 0 || j > 0);
+                            for (int p = 0; p < NP; ++p) {   // five small pairs into one accumulator, the leading pair into the other
+                                const uint32_t sa = base + split_a(p) * kSplitPartBytes, sb = base + (3 + split_b(p)) * kSplitPartBytes;
+                                const bool lead = p == NP - 1;
+#pragma unroll
+                                for (int j = 0; j < kTcBK / 16; ++j) {
+                                    const uint64_t da = A_MN ? tc::make_smem_desc(sa + j * 2048, 8192, 1024)
+                                                             : tc::make_smem_desc(sa + j * 32, 16, 1024);
+                                    const uint64_t db = B_MN ? tc::make_smem_desc(sb + j * 2048, 8192, 1024)
+                                                             : tc::make_smem_desc(sb + j * 32, 16, 1024);
+                                    tc::umma_f16(lead ? d_lead : d_small, da, db, idesc, st > 0 || j > 0 || (!lead && p > 0));
+                                }
+                            }
+                            tc::umma_commit(&empty_bar[stage]);
+                            if (++stage == kSplitStages) { stage = 0; phase ^= 1; }
                         }
-                        tc::umma_commit(&empty_bar[stage]);      // stage reusable once these MMAs have read it
-                        if (++stage == S::kStages) { stage = 0; phase ^= 1; }
+                    } else {
+                        for (uint32_t st = 0; st < num_kb; ++st) {
+                            if (!tc::mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
+                            tc::tc_fence_after_sync();
+                            const uint32_t sa = tc::smem_u32(stages + stage * S::kStageBytes), sb = sa + kTcABytes;
+#pragma unroll
+                            for (int j = 0; j < kTcBK / 16; ++j) {
+                                const uint64_t da = A_MN ? tc::make_smem_desc(sa + j * 2048, 8192, 1024)
+                                                         : tc::make_smem_desc(sa + j * 32, 16, 1024);
+                                const uint64_t db = B_MN ? tc::make_smem_desc(sb + j * 2048, 8192, 1024)
+                                                         : tc::make_smem_desc(sb + j * 32, 16, 1024);
+                                tc::umma_f16(d_tmem, da, db, idesc, st > 0 || j > 0);
+                            }
+                            tc::umma_commit(&empty_bar[stage]);      // stage reusable once these MMAs have read it
+                            if (++stage == S::kStages) { stage = 0; phase ^= 1; }
+                        }
                     }
                     if (!ok) break;
                     tc::umma_commit(&tmem_full[acc]);            // accumulator complete
@@ -266,10 +318,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     tc::tc_fence_after_sync();
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
-                        float t[32];
-                        tc::tmem_ld_32x32(tmem_base + ((quarter * 32) << 16) + acc * BN + half * (BN / 2) + h * 32, t);
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) part[h][j] += t[j];
+                        for (int which = 0; which < 2; ++which) {   // the leading pair's sum, then the small pairs'
+                            float t[32];
+                            tc::tmem_ld_32x32(tmem_base + ((quarter * 32) << 16) + acc * kBufCols + (1 - which) * BN + half * (BN / 2) + h * 32, t);
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) part[h][j] += t[j];
+                        }
                     }
                     tc::tc_fence_before_sync();
                     tc::mbar_arrive(&tmem_empty[acc]);
@@ -317,7 +372,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = first ? part[0][j] : part[1][j];
                 } else {
-                    tc::tmem_ld_32x32(tmem_base + ((quarter * 32) << 16) + acc * BN + c0, v);
+                    tc::tmem_ld_32x32(tmem_base + ((quarter * 32) << 16) + acc * kBufCols + c0, v);
                 }
 #pragma unroll
                 for (int j = 0; j < 32; ++j) buf[lane * 33 + j] = v[j];
